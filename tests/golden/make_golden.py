@@ -1,0 +1,324 @@
+#!/usr/bin/env python
+"""Generate the golden fixtures in this directory by running the *unmodified* xDiT reference.
+
+Run once, in a container that has the reference checkout (default ``/root/reference``,
+override with ``XDIT_REFERENCE``)::
+
+    python tests/golden/make_golden.py
+
+The reference's ``xfuser/model_executor/layers/usp.py`` and
+``xfuser/core/cache_manager/cache_manager.py`` are imported as they are.  Their heavy
+package ``__init__`` files (which need ``diffusers``) are skipped by pre-seeding bare
+namespace packages in ``sys.modules`` and a three-attribute ``diffusers`` stub.  Ranks are
+gloo processes on CPU.  Ulysses groups are contiguous ranks and ring groups are strided by
+the Ulysses degree (the yunchang convention the reference relies on,
+``xfuser/core/distributed/parallel_state.py:494-512``).
+
+Every case is written as one ``.npz`` holding the per-rank inputs and the per-rank outputs
+``USP()`` returned, so that tests can replay the same inputs through the oracle and through
+the CUDA path without the reference being present.
+"""
+from __future__ import annotations
+
+import importlib
+import os
+import sys
+import types
+
+import numpy as np
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+REF = os.environ.get("XDIT_REFERENCE", "/root/reference")
+
+
+# --------------------------------------------------------------------------------------
+# importing the reference without its heavy __init__ files
+# --------------------------------------------------------------------------------------
+def _seed_namespace(name: str, path: str) -> None:
+    mod = types.ModuleType(name)
+    mod.__path__ = [path]
+    sys.modules[name] = mod
+
+
+def import_reference():
+    """Return (usp, attention_backend, cache_manager, runtime_state) modules of the reference."""
+    if "diffusers" not in sys.modules:
+        stub = types.ModuleType("diffusers")
+        stub.__version__ = "0.35.2"
+        stub.DiffusionPipeline = object
+        sys.modules["diffusers"] = stub
+    if "xfuser" not in sys.modules:
+        _seed_namespace("xfuser", os.path.join(REF, "xfuser"))
+        _seed_namespace("xfuser.core", os.path.join(REF, "xfuser", "core"))
+        _seed_namespace("xfuser.model_executor", os.path.join(REF, "xfuser", "model_executor"))
+        _seed_namespace(
+            "xfuser.model_executor.layers", os.path.join(REF, "xfuser", "model_executor", "layers")
+        )
+    usp = importlib.import_module("xfuser.model_executor.layers.usp")
+    backend = importlib.import_module("xfuser.core.distributed.attention_backend")
+    cache = importlib.import_module("xfuser.core.cache_manager.cache_manager")
+    rts = importlib.import_module("xfuser.core.distributed.runtime_state")
+    return usp, backend, cache, rts
+
+
+class _FakeRuntimeConfig:
+    use_spargeattn_head_balance = False
+
+
+class FakeRuntimeState:
+    """The fields of the reference's runtime state that the hot path reads."""
+
+    def __init__(self, backend):
+        self.attention_backend = backend
+        self.runtime_config = _FakeRuntimeConfig()
+        self.num_pipeline_patch = 1
+        self.patch_mode = False
+        self.pipeline_patch_idx = 0
+        self.pp_patches_token_start_idx_local = [0]
+        self.pp_patches_token_num = []
+
+
+# --------------------------------------------------------------------------------------
+# USP cases
+# --------------------------------------------------------------------------------------
+# name, U, R, B, H, D, S_global(image), Sj(joint text), strategy, Sk_global (None => = S)
+USP_CASES = [
+    ("u2r1_none", 2, 1, 1, 4, 32, 96, 0, None, None),
+    ("u2r1_rear", 2, 1, 1, 4, 32, 96, 24, "rear", None),
+    ("u2r1_front", 2, 1, 2, 4, 32, 64, 16, "front", None),
+    ("u1r2_none", 1, 2, 1, 2, 32, 96, 0, None, None),
+    ("u1r2_rear", 1, 2, 1, 2, 32, 96, 24, "rear", None),
+    ("u1r2_front", 1, 2, 1, 2, 32, 96, 24, "front", None),
+    ("u2r2_none", 2, 2, 1, 4, 16, 128, 0, None, None),
+    ("u2r2_rear", 2, 2, 1, 4, 16, 128, 20, "rear", None),
+    ("u2r2_front", 2, 2, 1, 4, 16, 128, 20, "front", None),
+    ("u4r1_none", 4, 1, 1, 8, 16, 64, 0, None, None),
+    ("u1r4_rear", 1, 4, 1, 2, 16, 128, 12, "rear", None),
+    ("u2r1_cross", 2, 1, 1, 4, 32, 64, 0, None, 160),  # Sq != Sk
+    ("u1r1_rear", 1, 1, 1, 2, 32, 50, 14, "rear", None),
+    ("u2r1_combined", 2, 1, 1, 4, 32, 96, 0, None, None),  # combine_qkv_a2a=True
+]
+
+
+def _global_inputs(name, B, H, D, S, Sj, Sk):
+    seed = abs(hash_name(name)) % (2**31)
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(B, H, S, D, generator=g)
+    k = torch.randn(B, H, Sk, D, generator=g)
+    v = torch.randn(B, H, Sk, D, generator=g)
+    if Sj:
+        jq = torch.randn(B, H, Sj, D, generator=g)
+        jk = torch.randn(B, H, Sj, D, generator=g)
+        jv = torch.randn(B, H, Sj, D, generator=g)
+    else:
+        jq = jk = jv = None
+    return q, k, v, jq, jk, jv
+
+
+def hash_name(name: str) -> int:
+    h = 0
+    for ch in name:
+        h = (h * 131 + ord(ch)) & 0x7FFFFFFF
+    return h
+
+
+def _cpu_flash_lse(query, key, value, dropout_p, is_causal, attention_kwargs=None):
+    """An (out, lse) CPU op for ring cases: the stock LSE-returning back-ends are CUDA-only."""
+    out, lse = torch.ops.aten._scaled_dot_product_flash_attention_for_cpu(
+        query, key, value, dropout_p=dropout_p, is_causal=is_causal
+    )
+    return out, lse
+
+
+def _usp_worker(rank, world, port, cases, outdir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(1)
+    usp, backend, _cache, _rts = import_reference()
+    backend.ATTENTION_FUNCTION_REGISTRY[backend.AttentionBackendType.SDPA_FLASH] = _cpu_flash_lse
+
+    for (name, U, R, B, H, D, S, Sj, strat, Sk) in cases:
+        P = U * R
+        if P != world:
+            continue
+        Sk = S if Sk is None else Sk
+        # groups: ulysses = contiguous ranks, ring = stride U
+        uly_pg = ring_pg = None
+        for r in range(R):
+            ranks = list(range(r * U, (r + 1) * U))
+            pg = dist.new_group(ranks, backend="gloo")
+            if rank in ranks:
+                uly_pg = pg
+        for u in range(U):
+            ranks = list(range(u, P, U))
+            pg = dist.new_group(ranks, backend="gloo")
+            if rank in ranks:
+                ring_pg = pg
+        uly_rank, ring_rank = rank % U, rank // U
+
+        class PG:
+            ULYSSES_PG = uly_pg
+            RING_PG = ring_pg
+
+        usp.PROCESS_GROUP = PG
+        usp.get_ulysses_parallel_world_size = lambda U=U: U
+        usp.get_ulysses_parallel_rank = lambda r=uly_rank: r
+        usp.get_ring_parallel_world_size = lambda R=R: R
+        usp.get_sequence_parallel_world_size = lambda P=P: P
+        be = backend.AttentionBackendType.SDPA if R == 1 else backend.AttentionBackendType.SDPA_FLASH
+        state = FakeRuntimeState(be)
+        usp.get_runtime_state = lambda state=state: state
+
+        q, k, v, jq, jk, jv = _global_inputs(name, B, H, D, S, Sj, Sk)
+        # sequence shard of this SP rank (rank order = position in the sequence)
+        ql = q.chunk(P, dim=2)[rank]
+        kl = k.chunk(P, dim=2)[rank]
+        vl = v.chunk(P, dim=2)[rank]
+        kwargs = {}
+        if strat:
+            kwargs = dict(joint_query=jq, joint_key=jk, joint_value=jv, joint_strategy=strat)
+        if name.endswith("combined"):
+            kwargs["combine_qkv_a2a"] = True
+        out = usp.USP(ql, kl, vl, **kwargs)
+        gathered = [torch.empty_like(out) for _ in range(P)]
+        dist.all_gather(gathered, out.contiguous())
+        if rank == 0:
+            arrays = dict(
+                meta=np.array([U, R, B, H, D, S, Sj, Sk], dtype=np.int64),
+                strategy=np.array(strat or "none"),
+                q=q.numpy(), k=k.numpy(), v=v.numpy(),
+                out=np.stack([g.numpy() for g in gathered]),
+            )
+            if Sj:
+                arrays.update(jq=jq.numpy(), jk=jk.numpy(), jv=jv.numpy())
+            np.savez_compressed(os.path.join(outdir, f"usp_{name}.npz"), **arrays)
+        dist.barrier()
+    dist.destroy_process_group()
+
+
+# --------------------------------------------------------------------------------------
+# helper-level cases (single process): a2a re-layouts with the collective made an identity,
+# exactly the way the reference's own test does it (tests/layers/usp_test.py:270-271)
+# --------------------------------------------------------------------------------------
+def _layout_cases(outdir):
+    from unittest import mock
+
+    usp, _backend, _cache, _rts = import_reference()
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn(2, 4, 12, 8, generator=g)
+    q = torch.randn(2, 4, 12, 8, generator=g)
+    k = torch.randn(2, 4, 12, 8, generator=g)
+    v = torch.randn(2, 4, 12, 8, generator=g)
+    with mock.patch.object(usp, "get_ulysses_parallel_world_size", lambda: 2), mock.patch.object(
+        usp, "_sdpa_all_to_all_single", lambda t: t
+    ):
+        in_id = usp._ft_c_input_all_to_all(x)
+        out_id = usp._ft_c_output_all_to_all(x)
+        cq, ck, cv = usp._combined_qkv_all_to_all(q, k, v)
+    np.savez_compressed(
+        os.path.join(outdir, "layout_identity_a2a.npz"),
+        x=x.numpy(), in_id=in_id.numpy(), out_id=out_id.numpy(),
+        q=q.numpy(), k=k.numpy(), v=v.numpy(),
+        cq=cq.contiguous().numpy(), ck=ck.contiguous().numpy(), cv=cv.contiguous().numpy(),
+    )
+
+
+# --------------------------------------------------------------------------------------
+# PipeFusion stale-KV buffer cases (single process, fake runtime state)
+# --------------------------------------------------------------------------------------
+def _cache_cases(outdir):
+    _usp, _backend, cache, rts = import_reference()
+    import xfuser.core.distributed as xdist  # namespace stub or real package
+
+    class State:
+        num_pipeline_patch = 4
+        patch_mode = False
+        pipeline_patch_idx = 0
+        pp_patches_token_num = [6, 6, 6, 6]
+        pp_patches_token_start_idx_local = [0, 6, 12, 18, 24]
+
+    state = State()
+    rts.runtime_state_is_initialized = lambda: True
+    rts.get_runtime_state = lambda: state
+    cache.runtime_state_is_initialized = lambda: True
+
+    g = torch.Generator().manual_seed(11)
+    B, H, D = 1, 3, 8
+
+    # naive cache, slice_dim=2, [B,H,S,D] (how the PixArt processor calls it,
+    # xfuser/model_executor/layers/attention_processor.py:286-292)
+    mgr = cache.CacheManager()
+    layer = "L0"
+    mgr.register_cache_entry(layer, "attn", "naive_cache")
+    S = 24
+    k0 = torch.randn(B, H, S, D, generator=g)
+    v0 = torch.randn(B, H, S, D, generator=g)
+    state.patch_mode = False
+    ko, vo = mgr.update_and_get_kv_cache([k0, v0], layer, slice_dim=2, layer_type="attn")
+    rec = dict(k0=k0.numpy(), v0=v0.numpy(), warm_k=ko.contiguous().numpy().copy(),
+               warm_v=vo.contiguous().numpy().copy())
+    state.patch_mode = True
+    for p in [2, 0, 3]:
+        state.pipeline_patch_idx = p
+        kp = torch.randn(B, H, 6, D, generator=g)
+        vp = torch.randn(B, H, 6, D, generator=g)
+        ko, vo = mgr.update_and_get_kv_cache([kp, vp], layer, slice_dim=2, layer_type="attn")
+        rec[f"kp{p}"] = kp.numpy()
+        rec[f"vp{p}"] = vp.numpy()
+        rec[f"k_after{p}"] = ko.contiguous().numpy().copy()
+        rec[f"v_after{p}"] = vo.contiguous().numpy().copy()
+    rec["patch_order"] = np.array([2, 0, 3])
+    rec["token_start"] = np.array(state.pp_patches_token_start_idx_local)
+    np.savez_compressed(os.path.join(outdir, "kvcache_naive.npz"), **rec)
+
+    # sequence-parallel cache (U=2), slice_dim=1 on [B,S,H,D] as usp.py:191-203 calls it
+    import xfuser.core.distributed as xd
+    U = 2
+    xd.get_ulysses_parallel_world_size = lambda: U
+    xd.get_runtime_state = lambda: state
+    mgr = cache.CacheManager()
+    mgr.register_cache_entry(layer, "attn", "sequence_parallel_attn_cache")
+    state.patch_mode = False
+    state.pipeline_patch_idx = 0
+    Sfull = U * 24
+    k0 = torch.randn(B, Sfull, H, D, generator=g)
+    v0 = torch.randn(B, Sfull, H, D, generator=g)
+    ko, vo = mgr.update_and_get_kv_cache([k0, v0], layer, slice_dim=1, layer_type="attn")
+    rec = dict(k0=k0.numpy(), v0=v0.numpy(), warm_k=ko.contiguous().numpy().copy(),
+               warm_v=vo.contiguous().numpy().copy(), U=np.array(U))
+    state.patch_mode = True
+    for p in [1, 3, 0]:
+        state.pipeline_patch_idx = p
+        kp = torch.randn(B, U * 6, H, D, generator=g)
+        vp = torch.randn(B, U * 6, H, D, generator=g)
+        ko, vo = mgr.update_and_get_kv_cache([kp, vp], layer, slice_dim=1, layer_type="attn")
+        rec[f"kp{p}"] = kp.numpy()
+        rec[f"vp{p}"] = vp.numpy()
+        rec[f"k_after{p}"] = ko.contiguous().numpy().copy()
+        rec[f"v_after{p}"] = vo.contiguous().numpy().copy()
+    rec["patch_order"] = np.array([1, 3, 0])
+    rec["token_start"] = np.array(state.pp_patches_token_start_idx_local)
+    rec["token_num"] = np.array(state.pp_patches_token_num)
+    np.savez_compressed(os.path.join(outdir, "kvcache_sp.npz"), **rec)
+
+
+def main():
+    outdir = HERE
+    port = 29611
+    for world in (1, 2, 4):
+        cases = [c for c in USP_CASES if c[1] * c[2] == world]
+        if not cases:
+            continue
+        mp.spawn(_usp_worker, args=(world, port, cases, outdir), nprocs=world, join=True)
+        port += 1
+    _layout_cases(outdir)
+    _cache_cases(outdir)
+    print("golden fixtures written to", outdir)
+
+
+if __name__ == "__main__":
+    main()

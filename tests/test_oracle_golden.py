@@ -1,0 +1,167 @@
+"""The numpy oracle against fixtures produced by the unmodified reference
+(tests/golden/make_golden.py).  This is what pins the oracle."""
+import glob
+import os
+
+import numpy as np
+import pytest
+
+from oracle import usp_oracle as O
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+USP_FILES = sorted(glob.glob(os.path.join(HERE, "golden", "usp_*.npz")))
+
+
+def _load(path):
+    z = np.load(path)
+    U, R, B, H, D, S, Sj, Sk = [int(x) for x in z["meta"]]
+    strat = str(z["strategy"])
+    return z, U, R, B, H, D, S, Sj, Sk, (None if strat == "none" else strat)
+
+
+def test_fixture_inventory():
+    assert len(USP_FILES) >= 14
+
+
+@pytest.mark.parametrize("path", USP_FILES, ids=[os.path.basename(p)[4:-4] for p in USP_FILES])
+def test_usp_matches_reference(path):
+    z, U, R, B, H, D, S, Sj, Sk, strat = _load(path)
+    kw = {}
+    if strat:
+        kw = dict(joint_query=z["jq"], joint_key=z["jk"], joint_value=z["jv"], joint_strategy=strat)
+    if path.endswith("combined.npz"):
+        kw["combine_qkv_a2a"] = True
+    outs = O.usp_from_global(z["q"], z["k"], z["v"], U, R, **kw)
+    ref = z["out"]
+    assert ref.shape[0] == U * R
+    for g in range(U * R):
+        assert outs[g].shape == ref[g].shape
+        np.testing.assert_allclose(outs[g], ref[g], atol=2e-5, rtol=1e-4)
+
+
+@pytest.mark.parametrize("path", USP_FILES, ids=[os.path.basename(p)[4:-4] for p in USP_FILES])
+def test_usp_equals_dense_attention(path):
+    """Layout-independent property: every rank's rows equal dense attention over all keys."""
+    z, U, R, B, H, D, S, Sj, Sk, strat = _load(path)
+    P = U * R
+    q, k, v = z["q"], z["k"], z["v"]
+    if strat:
+        kfull = np.concatenate([k, z["jk"]], axis=2)
+        vfull = np.concatenate([v, z["jv"]], axis=2)
+    else:
+        kfull, vfull = k, v
+    for g in range(P):
+        ql = np.array_split(q, P, axis=2)[g]
+        if strat:
+            ql = O.concat_joint(ql, z["jq"], strat)
+        dense, _ = O.attention_dense(ql, kfull, vfull)
+        np.testing.assert_allclose(z["out"][g], dense, atol=2e-5, rtol=1e-4)
+
+
+def test_layout_identity_a2a(golden_dir):
+    """a2a re-layouts with the collective replaced by an identity, as the reference's own
+    test does (tests/layers/usp_test.py:268-307)."""
+    z = np.load(os.path.join(golden_dir, "layout_identity_a2a.npz"))
+    x = z["x"]
+    b, h, s, d = x.shape
+    U = 2
+    # identity collective == every rank holds the same x and receives its own flat buffer
+    y = np.ascontiguousarray(np.transpose(x, (1, 0, 2, 3)))
+    y = y.reshape(U, h // U, b, -1, d).transpose(2, 1, 0, 3, 4).reshape(b, h // U, -1, d)
+    np.testing.assert_array_equal(y, z["in_id"])
+    y = np.ascontiguousarray(np.transpose(x, (2, 0, 1, 3)))
+    y = y.reshape(U, s // U, b, -1, d).transpose(2, 0, 3, 1, 4).reshape(b, -1, s // U, d)
+    np.testing.assert_array_equal(y, z["out_id"])
+
+
+def test_combined_equals_separate():
+    rng = np.random.default_rng(0)
+    U = 2
+    qs = [rng.standard_normal((2, 4, 6, 8)) for _ in range(U)]
+    ks = [rng.standard_normal((2, 4, 6, 8)) for _ in range(U)]
+    vs = [rng.standard_normal((2, 4, 6, 8)) for _ in range(U)]
+    cq, ck, cv = O.combined_qkv_all_to_all(qs, ks, vs)
+    for a, b in zip(cq, O.input_all_to_all(qs)):
+        np.testing.assert_array_equal(a, b)
+    for a, b in zip(ck, O.input_all_to_all(ks)):
+        np.testing.assert_array_equal(a, b)
+    for a, b in zip(cv, O.input_all_to_all(vs)):
+        np.testing.assert_array_equal(a, b)
+
+
+def test_output_a2a_inverts_input_a2a():
+    rng = np.random.default_rng(1)
+    U = 4
+    xs = [rng.standard_normal((1, 8, 5, 4)) for _ in range(U)]
+    back = O.output_all_to_all(O.input_all_to_all(xs))
+    for a, b in zip(xs, back):
+        np.testing.assert_array_equal(a, b)
+
+
+def test_merge_is_exact_split_softmax():
+    rng = np.random.default_rng(2)
+    q = rng.standard_normal((1, 2, 7, 8))
+    k = rng.standard_normal((1, 2, 33, 8))
+    v = rng.standard_normal((1, 2, 33, 8))
+    full, lse_full = O.attention_dense(q, k, v)
+    out = lse = None
+    for lo, hi in ((0, 10), (10, 11), (11, 33)):
+        bo, bl = O.attention_dense(q, k[:, :, lo:hi], v[:, :, lo:hi])
+        out, lse = O.merge_out_lse(out, lse, bo, bl)
+    np.testing.assert_allclose(out, full, atol=1e-12)
+    np.testing.assert_allclose(lse, lse_full, atol=1e-12)
+
+
+def _replay_cache(z, cache_type, U, slice_dim):
+    c = O.KVCacheOracle(cache_type, U=U)
+    ts = [int(x) for x in z["token_start"]]
+    tn = [ts[i + 1] - ts[i] for i in range(len(ts) - 1)]
+    k, v = c.update(z["k0"], z["v0"], slice_dim, 4, False, 0, ts, tn)
+    np.testing.assert_array_equal(k, z["warm_k"])
+    np.testing.assert_array_equal(v, z["warm_v"])
+    for p in [int(x) for x in z["patch_order"]]:
+        k, v = c.update(z[f"kp{p}"], z[f"vp{p}"], slice_dim, 4, True, p, ts, tn)
+        np.testing.assert_array_equal(k, z[f"k_after{p}"])
+        np.testing.assert_array_equal(v, z[f"v_after{p}"])
+
+
+def test_kvcache_naive(golden_dir):
+    _replay_cache(np.load(os.path.join(golden_dir, "kvcache_naive.npz")), "naive", 1, 2)
+
+
+def test_kvcache_sp(golden_dir):
+    z = np.load(os.path.join(golden_dir, "kvcache_sp.npz"))
+    _replay_cache(z, "sp", int(z["U"]), 1)
+
+
+def test_legacy_bshd_equals_usp():
+    """The identity the reference asserts in tests/layers/usp_test.py:211-265: the BSHD layer
+    equals USP on transposed tensors, with and without joint tensors."""
+    rng = np.random.default_rng(3)
+    U, R = 2, 2
+    P = U * R
+    B, H, S, D, Sj = 1, 4, 32, 8, 6
+    q, k, v = (rng.standard_normal((B, H, S, D)) for _ in range(3))
+    jq, jk, jv = (rng.standard_normal((B, H, Sj, D)) for _ in range(3))
+    t = lambda x: np.transpose(x, (0, 2, 1, 3))
+    for strat in (None, "rear", "front"):
+        kw = dict(joint_query=jq, joint_key=jk, joint_value=jv, joint_strategy=strat) if strat else {}
+        a = O.usp_from_global(q, k, v, U, R, **kw)
+        kw2 = dict(joint_query=t(jq), joint_key=t(jk), joint_value=t(jv), joint_strategy=strat) if strat else {}
+        b = O.long_context_attention_bshd(np.array_split(t(q), P, axis=1), np.array_split(t(k), P, axis=1),
+                                          np.array_split(t(v), P, axis=1), U, R, **kw2)
+        for g in range(P):
+            np.testing.assert_allclose(t(b[g]), a[g], atol=1e-12)
+
+
+def test_causal_ring_equals_dense_causal():
+    """tests/core/test_ring_flash_attn.py:78-103: causal ring == causal dense on the global
+    sequence (fp16 (1,128,4,32) there; float64 here)."""
+    rng = np.random.default_rng(4)
+    R = 2
+    q, k, v = (rng.standard_normal((1, 128, 4, 32)) for _ in range(3))
+    outs, _ = O.ring_flash_attn_bshd(np.array_split(q, R, axis=1), np.array_split(k, R, axis=1),
+                                     np.array_split(v, R, axis=1), causal=True)
+    t = lambda x: np.transpose(x, (0, 2, 1, 3))
+    dense, _ = O.attention_dense(t(q), t(k), t(v), causal=True)
+    np.testing.assert_allclose(np.concatenate(outs, axis=1), t(dense), atol=1e-12)
