@@ -1,0 +1,178 @@
+/*
+ * xdit_b200 -- C ABI of the B200 (sm_100a) kernels behind xDiT's Unified-Sequence-Parallel
+ * (USP) attention path.
+ *
+ * The reference is pure Python and has no FFI of its own; each entry point below replaces a
+ * run of torch calls in the reference (cited as file:line inside the xDiT source tree) and
+ * is what a Python/ctypes binding of that path binds.
+ *
+ * Conventions
+ *   - every function returns 0 on success, a negative XDIT_E_* code for a rejected argument
+ *     and a positive value (a cudaError_t) when the CUDA runtime reported an error;
+ *     xdit_last_error_string() gives a human-readable reason for the calling thread;
+ *   - no function allocates or frees device memory, and none synchronises the device: work is
+ *     enqueued on `stream` (a cudaStream_t passed as void*; NULL is the legacy default stream);
+ *   - pointers are device pointers unless stated otherwise; the caller keeps ownership;
+ *   - strides are in ELEMENTS of the tensor's dtype; the innermost (head_dim) axis is
+ *     contiguous everywhere;
+ *   - kernels are built for sm_100a only; on any other device calls fail with
+ *     XDIT_E_UNSUPPORTED_DEVICE.
+ */
+#ifndef XDIT_B200_H_
+#define XDIT_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define XDIT_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define XDIT_API __attribute__((visibility("default")))
+#else
+#define XDIT_API
+#endif
+
+enum xdit_dtype { XDIT_BF16 = 0, XDIT_F16 = 1, XDIT_F32 = 2 };
+
+enum xdit_status {
+  XDIT_OK = 0,
+  XDIT_E_NULL = -1,               /* a required pointer is NULL */
+  XDIT_E_SHAPE = -2,              /* a size is zero, negative or out of the supported range */
+  XDIT_E_ALIGN = -3,              /* a pointer or stride breaks an alignment rule */
+  XDIT_E_DTYPE = -4,              /* unknown or unsupported dtype for this entry point */
+  XDIT_E_UNSUPPORTED_DEVICE = -5, /* current device is not sm_100 */
+  XDIT_E_KERNEL_TIMEOUT = -6,     /* a bounded wait inside a kernel gave up (see xdit_attn_status) */
+  XDIT_E_DRIVER = -7              /* a CUDA driver entry point could not be resolved */
+};
+
+struct xdit_caps {
+  int abi_version;
+  int device;
+  int sm_major, sm_minor;
+  int sm_count;
+  int max_smem_per_block;
+  int supported; /* 1 when the device is sm_100 and the tcgen05 path can run */
+};
+
+/* Diagnostics (proposed in place of Python exceptions raised by the reference). */
+XDIT_API int xdit_query_caps(struct xdit_caps* out);
+XDIT_API const char* xdit_last_error_string(void);
+
+/* A sequence as the attention kernel sees it: `nseg` equally long segments of `seg_len`
+ * rows.  After a Ulysses all-to-all every source rank's rows form one segment of the receive
+ * buffer; a plain tensor is one segment.  Row r of segment g of head h of batch b starts at
+ * ptr + b*stride_b + h*stride_h + g*stride_seg + r*stride_row  (elements). */
+struct xdit_seq {
+  const void* ptr;
+  int64_t stride_b, stride_h, stride_seg, stride_row;
+  int32_t nseg, seg_len;
+};
+
+/* Dense softmax attention forward, with the joint (replicated text) K/V as a second key/value
+ * source and the ring-step merge fused into the epilogue.
+ *
+ * Replaces: the back-end call (q,k,v)->(out,lse) xfuser/core/distributed/attention_backend.py:492-566,
+ * :887-918; torch.cat of joint K/V xfuser/model_executor/layers/usp.py:218-245 and
+ * xfuser/core/long_ctx_attention/ring/ring_flash_attn.py:89-102; the post-all-to-all re-layout
+ * copies usp.py:107,132; the partial-result merge (torch _SDPAMerger._merge_one; yunchang
+ * update_out_and_lse called at ring_flash_attn.py:138).
+ *
+ * out has the segmentation of q.  lse/lse_acc are [B,H,Sq] fp32 contiguous and o_acc is
+ * [B,H,Sq,D] fp32 contiguous, with Sq = q.nseg*q.seg_len rows in segment-major order.
+ *   acc_in  != 0 : merge this call's (out,lse) into (o_acc,lse_acc) read from memory;
+ *   acc_out != 0 : write the (merged) result to (o_acc,lse_acc) in fp32, leave `out` untouched;
+ *   acc_out == 0 : write the (merged) result to `out` in `dtype` (and to `lse` when not NULL).
+ * causal != 0 masks key j > query i (top-left aligned), one segment only. */
+struct xdit_attn_params {
+  int32_t dtype; /* xdit_dtype of q,k,v,out */
+  int32_t B, H, D;
+  struct xdit_seq q;   /* queries */
+  struct xdit_seq k, v; /* main keys / values: same nseg and seg_len */
+  struct xdit_seq k2, v2; /* joint keys / values (ptr NULL when absent): nseg must be 1 */
+  void* out;
+  int64_t out_stride_b, out_stride_h, out_stride_seg, out_stride_row;
+  float* lse;     /* optional */
+  float* o_acc;   /* required when acc_in or acc_out */
+  float* lse_acc; /* required when acc_in or acc_out */
+  int32_t acc_in, acc_out;
+  int32_t causal;
+  float softmax_scale; /* <= 0 selects D^-1/2 */
+  int32_t force_generic; /* != 0: use the CUDA-core kernel even where the tcgen05 kernel applies */
+  int32_t* status;       /* optional device int32: set non-zero when a bounded wait gave up */
+};
+XDIT_API int xdit_attn_fwd(const struct xdit_attn_params* p, void* stream);
+/* Which kernel xdit_attn_fwd would run for these parameters: 1 = tcgen05/TMEM/TMA kernel,
+ * 0 = CUDA-core kernel, negative = the error the call would return. */
+XDIT_API int xdit_attn_which(const struct xdit_attn_params* p);
+
+/* Ulysses input pack: [B,H,s,D] (any strides) plus optional joint rows -> the all-to-all send
+ * buffer, peer-major.  For peer p the block at dst + p*dst_peer_stride holds
+ * [H/U][B][s + s_joint][D] contiguous, i.e. heads [p*H/U,(p+1)*H/U) of the source; joint rows
+ * are placed after (joint_front == 0) or before (joint_front != 0) the s source rows.
+ * Up to XDIT_MAX_PACK_JOBS tensors (q, k, v) are packed by one launch.
+ *
+ * Replaces: x.permute(1,0,2,3).contiguous() usp.py:105, the stack/permute/contiguous of
+ * usp.py:122-126 and the query concat usp.py:294 (hybrid/attn_layer.py:136-158, :185). */
+#define XDIT_MAX_PACK_JOBS 4
+struct xdit_pack_job {
+  const void* src;
+  int64_t src_stride_b, src_stride_h, src_stride_row;
+  const void* joint; /* optional [B,H,s_joint,D] */
+  int64_t joint_stride_b, joint_stride_h, joint_stride_row;
+  void* dst;
+  int64_t dst_peer_stride; /* elements between consecutive peers' blocks */
+  int32_t s, s_joint, joint_front;
+};
+XDIT_API int xdit_ulysses_pack(const struct xdit_pack_job* jobs, int32_t njobs, int32_t dtype, int32_t B,
+                      int32_t H, int32_t D, int32_t U, void* stream);
+
+/* Ulysses output pack in the reference's own wire layout: [B,Hl,S,D] (any strides) ->
+ * send buffer [S][B][Hl][D] contiguous (peer p's block = rows [p*S/U,(p+1)*S/U)), and the
+ * inverse on the receive side: [U][s][B][Hl][D] -> [B][U*Hl][s][D] contiguous.
+ * Replaces: usp.py:147 (permute(2,0,1,3).contiguous()) and usp.py:149. */
+XDIT_API int xdit_ulysses_pack_out(const void* src, int64_t stride_b, int64_t stride_h, int64_t stride_row,
+                          void* dst, int32_t dtype, int32_t B, int32_t Hl, int32_t S, int32_t D,
+                          void* stream);
+XDIT_API int xdit_ulysses_unpack_out(const void* recv, void* dst, int32_t dtype, int32_t B, int32_t Hl,
+                            int32_t s, int32_t D, int32_t U, void* stream);
+
+/* Ulysses input unpack in the reference's wire layout: recv [U][Hl][B][s][D] -> [B][Hl][U*s][D]
+ * contiguous.  Replaces usp.py:107 for callers that need the materialised tensor. */
+XDIT_API int xdit_ulysses_unpack_in(const void* recv, void* dst, int32_t dtype, int32_t B, int32_t Hl,
+                           int32_t s, int32_t D, int32_t U, void* stream);
+
+/* PipeFusion stale-KV patch update: overwrite rows [row_start, row_start + nseg*n) of the
+ * persistent K and V caches (attention layout, strides given) with fresh rows.  The fresh rows
+ * come as `nseg` segments of `n` rows (one segment per Ulysses source rank; nseg = 1 without
+ * sequence parallelism); segment g lands at cache rows row_start + g*n.
+ *
+ * Replaces: torch.cat(new_kv,-1) cache_manager.py:76, the slice-assign of
+ * cache_manager.py:127-133 / :172-192 -> _update_kv_in_dim :196-219, torch.chunk :99 and the
+ * two .contiguous() copies of usp.py:201-202 / ring_flash_attn.py:80-81. */
+struct xdit_kv_patch_params {
+  int32_t dtype, B, H, D;
+  void* k_cache; void* v_cache;
+  int64_t cache_stride_b, cache_stride_h, cache_stride_row; /* same for both caches */
+  int32_t cache_rows;
+  struct xdit_seq k_new, v_new; /* nseg segments of seg_len = n rows */
+  int32_t row_start;
+};
+XDIT_API int xdit_kv_patch_update(const struct xdit_kv_patch_params* p, void* stream);
+
+/* Stand-alone online-softmax merge of a partial result into fp32 accumulators:
+ *   o_acc <- o_acc - sigmoid(lse_b - lse_acc) * (o_acc - out_b);
+ *   lse_acc <- lse_acc - logsigmoid(lse_acc - lse_b)
+ * over `rows` rows of D elements; first != 0 initialises the accumulators from the block.
+ * out_final (optional, dtype) receives the merged rows cast to `dtype`.
+ * Replaces: torch _SDPAMerger.step / yunchang update_out_and_lse (ring_flash_attn.py:138). */
+XDIT_API int xdit_merge_out_lse(float* o_acc, float* lse_acc, const void* out_b, const float* lse_b,
+                       void* out_final, int32_t dtype, int64_t rows, int32_t D, int32_t first,
+                       void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* XDIT_B200_H_ */

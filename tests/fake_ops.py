@@ -1,0 +1,102 @@
+"""CPU stand-ins for ``xdit_b200.ops`` used ONLY by host-logic tests: they let the Python
+orchestration (buffer layouts, strided views, all-to-all and ring schedules) run under gloo on
+a machine without a GPU.  The arithmetic comes from the oracle.  Never imported by the package."""
+import numpy as np
+import torch
+
+from oracle import usp_oracle as O
+
+
+def _flat4(x):
+    if x is None:
+        return None
+    if x.dim() == 5:
+        B, H, G, L, D = x.shape
+        return x.reshape(B, H, G * L, D)
+    return x
+
+
+def _np(x):
+    return x.detach().to(torch.float64).numpy()
+
+
+def attn_fwd(q, k, v, k2=None, v2=None, *, out=None, lse=None, o_acc=None, lse_acc=None, acc_in=False,
+             acc_out=False, causal=False, scale=None, force_generic=False, want_lse=False):
+    q4, k4, v4 = _flat4(q), _flat4(k), _flat4(v)
+    if k2 is not None:
+        k4 = torch.cat([k4, k2], dim=2)
+        v4 = torch.cat([v4, v2], dim=2)
+    o, l = O.attention_dense(_np(q4), _np(k4), _np(v4), scale=scale, causal=causal)
+    if acc_in:
+        o, l = O.merge_out_lse(_np(o_acc), _np(lse_acc), o, l)
+    if acc_out:
+        o_acc.copy_(torch.from_numpy(o).to(o_acc.dtype))
+        lse_acc.copy_(torch.from_numpy(l).to(lse_acc.dtype))
+        return out, lse
+    if out is None:
+        out = torch.empty(q.shape, dtype=q.dtype)
+    out.copy_(torch.from_numpy(o).to(q.dtype).reshape(out.shape))
+    if lse is None and want_lse:
+        lse = torch.empty(q4.shape[:3], dtype=torch.float32)
+    if lse is not None:
+        lse.copy_(torch.from_numpy(l).to(torch.float32))
+    return out, lse
+
+
+def ulysses_pack(items, U):
+    for it in items:
+        src, joint, dst, stride = it["src"], it.get("joint"), it["dst"], it["peer_stride"]
+        x = src
+        if joint is not None:
+            x = torch.cat([joint, src], 2) if it.get("front") else torch.cat([src, joint], 2)
+        B, H, rows, D = x.shape
+        Hl = H // U
+        blk = Hl * B * rows * D
+        for p in range(U):
+            part = x[:, p * Hl:(p + 1) * Hl].permute(1, 0, 2, 3).reshape(-1)
+            dst[p * stride:p * stride + blk].copy_(part)
+
+
+def ulysses_unpack_in(recv, B, Hl, s, D, U):
+    return recv.reshape(U, Hl, B, s, D).permute(2, 1, 0, 3, 4).reshape(B, Hl, U * s, D).contiguous()
+
+
+def ulysses_pack_out(x):
+    return x.permute(2, 0, 1, 3).contiguous()
+
+
+def ulysses_unpack_out(recv, B, Hl, s, D, U):
+    return recv.reshape(U, s, B, Hl, D).permute(2, 0, 3, 1, 4).reshape(B, U * Hl, s, D).contiguous()
+
+
+def kv_patch_update(k_cache, v_cache, k_new, v_new, row_start):
+    kn, vn = _flat4(k_new), _flat4(v_new)
+    n = kn.shape[2]
+    if row_start < 0 or row_start + n > k_cache.shape[2]:
+        raise RuntimeError("rows outside the cache")
+    k_cache[:, :, row_start:row_start + n] = kn
+    v_cache[:, :, row_start:row_start + n] = vn
+
+
+def merge_out_lse(o_acc, lse_acc, out_b, lse_b, first, out_final=None):
+    if first:
+        o, l = _np(out_b), _np(lse_b)
+    else:
+        o, l = O.merge_out_lse(_np(o_acc), _np(lse_acc), _np(out_b), _np(lse_b))
+    o_acc.copy_(torch.from_numpy(np.asarray(o)).to(o_acc.dtype))
+    lse_acc.copy_(torch.from_numpy(np.asarray(l)).to(lse_acc.dtype))
+    if out_final is not None:
+        out_final.copy_(o_acc.to(out_final.dtype))
+
+
+def install(monkeypatch_or_none=None):
+    """Replace the CUDA wrappers of ``xdit_b200.ops`` with the CPU stand-ins above."""
+    import xdit_b200.ops as ops
+
+    names = ["attn_fwd", "ulysses_pack", "ulysses_unpack_in", "ulysses_pack_out", "ulysses_unpack_out",
+             "kv_patch_update", "merge_out_lse"]
+    for n in names:
+        if monkeypatch_or_none is not None:
+            monkeypatch_or_none.setattr(ops, n, globals()[n])
+        else:
+            setattr(ops, n, globals()[n])

@@ -1,0 +1,704 @@
+// Flash-attention forward for sm_100a: tcgen05.mma with TMEM accumulators, operands staged by
+// TMA, warp-specialised online softmax.  bf16/fp16, head_dim a multiple of 8 up to 128.
+//
+// One CTA owns two query tiles of 128 rows and walks all key/value tiles of 128 rows.
+//   warps 0-3  softmax group for query tile 0   (one thread per query row)
+//   warps 4-7  softmax group for query tile 1
+//   warp  8    issues every tcgen05.mma (one lane) and owns the TMEM allocation
+//   warp  9    issues every TMA load (one lane)
+// The tensor core alternates between the two query tiles, so that one tile's softmax runs while
+// the other tile's S = Q K^T and O += P V are in flight.
+//
+// TMEM (512 columns x 128 lanes, fp32):  S0 [0,128)  S1 [128,256)  O0 [256,384)  O1 [384,512).
+// P (bf16/fp16, two per column) overwrites columns [0,64) of its S tile and is fed to the second
+// GEMM as the A operand straight from TMEM.
+//
+// Shared memory: Q 2 tiles, then a ring of K/V stages (K0,V0,K1,V1,...).  Every tile is stored
+// as head_dim slabs of 64 elements: slab s holds [rows][64] with 128-byte rows in the 128-byte
+// swizzle, which is both what a TMA box {64 elements, 64 rows} writes and what the UMMA
+// descriptors read (K-major for Q and K, MN-major for V).
+//
+// Sequences are lists of 64-row chunks: a tensor after a Ulysses all-to-all is `nseg` segments
+// (one per source rank) and each segment is cut into chunks of its own, the joint (text) K/V
+// follow as a second tensor map.  Rows past a segment's end are zero-filled by TMA and masked
+// to -inf before the softmax.  Because keys may be visited in any order, no re-layout copy is
+// needed between the all-to-all and this kernel.
+//
+// Every wait on an mbarrier is bounded in time; when one gives up the CTA raises a flag in
+// shared memory, all roles leave their loops, outstanding copies and MMAs are drained with
+// bounded waits, TMEM is freed and *status is set.
+#include <cuda.h>
+
+#include <cmath>
+#include <cstring>
+#include <mutex>
+
+#include "common.cuh"
+
+namespace xdit {
+namespace {
+
+constexpr int kChunk = 64;
+constexpr int kTile = 128;
+constexpr int kThreads = 320;
+constexpr int kSlabBytes = kTile * 128;       // one 64-element slab of a 128-row tile
+constexpr int kBoxBytes = kChunk * 128;       // one TMA box: 64 rows x 64 elements
+constexpr uint64_t kWaitLimitNs = 4000000000ull;
+
+struct alignas(64) Sm100Args {
+  CUtensorMap tm_q, tm_k, tm_v, tm_k2, tm_v2;
+  int32_t q_seg_len, q_cps, q_chunks;
+  int32_t k_seg_len, k_cps, k_chunks_main, k2_len, kv_chunks, n_kv_tiles;
+  int32_t H, D, dk16, dv_n;
+  int32_t sq_total;
+  float scale_log2;
+  void* out;
+  int64_t out_stride_b, out_stride_h, out_stride_seg, out_stride_row;
+  float* lse;
+  float* o_acc;
+  float* lse_acc;
+  int32_t acc_in, acc_out;
+  int32_t* status;
+};
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait.  Returns false when the CTA is aborting or the time limit passed (and then
+// raises the abort flag itself, recording `code`).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  for (uint32_t it = 0;; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if ((it & 63) == 63 && global_timer_ns() - t0 > kWaitLimitNs) {
+      *abort_flag = code;
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int c0,
+                                            int c1, int c2, int c3, int c4) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(dst), "l"(tm), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(acc) : "memory");
+}
+#define XDIT_R32(a, o) \
+  "=r"(a[o + 0]), "=r"(a[o + 1]), "=r"(a[o + 2]), "=r"(a[o + 3]), "=r"(a[o + 4]), "=r"(a[o + 5]), "=r"(a[o + 6]), \
+  "=r"(a[o + 7]), "=r"(a[o + 8]), "=r"(a[o + 9]), "=r"(a[o + 10]), "=r"(a[o + 11]), "=r"(a[o + 12]),                \
+  "=r"(a[o + 13]), "=r"(a[o + 14]), "=r"(a[o + 15]), "=r"(a[o + 16]), "=r"(a[o + 17]), "=r"(a[o + 18]),              \
+  "=r"(a[o + 19]), "=r"(a[o + 20]), "=r"(a[o + 21]), "=r"(a[o + 22]), "=r"(a[o + 23]), "=r"(a[o + 24]),              \
+  "=r"(a[o + 25]), "=r"(a[o + 26]), "=r"(a[o + 27]), "=r"(a[o + 28]), "=r"(a[o + 29]), "=r"(a[o + 30]), "=r"(a[o + 31])
+#define XDIT_W32(a, o) \
+  "r"(a[o + 0]), "r"(a[o + 1]), "r"(a[o + 2]), "r"(a[o + 3]), "r"(a[o + 4]), "r"(a[o + 5]), "r"(a[o + 6]),    \
+  "r"(a[o + 7]), "r"(a[o + 8]), "r"(a[o + 9]), "r"(a[o + 10]), "r"(a[o + 11]), "r"(a[o + 12]), "r"(a[o + 13]), \
+  "r"(a[o + 14]), "r"(a[o + 15]), "r"(a[o + 16]), "r"(a[o + 17]), "r"(a[o + 18]), "r"(a[o + 19]),             \
+  "r"(a[o + 20]), "r"(a[o + 21]), "r"(a[o + 22]), "r"(a[o + 23]), "r"(a[o + 24]), "r"(a[o + 25]),             \
+  "r"(a[o + 26]), "r"(a[o + 27]), "r"(a[o + 28]), "r"(a[o + 29]), "r"(a[o + 30]), "r"(a[o + 31])
+// 32 lanes x 32 consecutive columns -> 32 registers per thread (thread i = lane base + i)
+#define XDIT_TMEM_LD32(a, o, taddr)                                                                      \
+  asm volatile(                                                                                          \
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "                                                          \
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "                           \
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"          \
+      : XDIT_R32(a, o) : "r"(taddr) : "memory")
+#define XDIT_TMEM_ST32(a, o, taddr)                                                                      \
+  asm volatile(                                                                                          \
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "                                                   \
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "                           \
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31};"                 \
+      ::XDIT_W32(a, o), "r"(taddr) : "memory")
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Shared-memory matrix descriptors (sm_100 format: version 1 at bit 46, 128-byte swizzle = 2 at
+// bits 61-63, offsets in 16-byte units).
+// K-major operand (Q, K): rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t saddr) {
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// MN-major operand (V: N = head_dim contiguous, K = key rows): 64-element groups of N are one
+// slab apart (leading offset), 8-row groups of K are 1024 bytes apart (stride offset).
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t saddr) {
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(kSlabBytes >> 4) << 16) |
+         ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// Instruction descriptor, kind::f16: D fp32, A/B bf16 (1) or fp16 (0), M = 128.
+__device__ __forceinline__ uint32_t make_idesc(bool bf16, bool b_mn_major, int n) {
+  const uint32_t fmt = bf16 ? 1u : 0u;
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(kTile >> 4) << 24);
+}
+
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  if constexpr (BF16) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  } else {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+}
+
+struct ChunkLoc {
+  int src, seg, row0, valid;
+};
+__device__ __forceinline__ ChunkLoc kv_chunk(const Sm100Args& a, int c) {
+  ChunkLoc r;
+  if (c < a.k_chunks_main) {
+    r.src = 0;
+    r.seg = c / a.k_cps;
+    r.row0 = (c - r.seg * a.k_cps) * kChunk;
+    r.valid = min(kChunk, a.k_seg_len - r.row0);
+  } else if (c < a.kv_chunks) {
+    r.src = 1;
+    r.seg = 0;
+    r.row0 = (c - a.k_chunks_main) * kChunk;
+    r.valid = min(kChunk, a.k2_len - r.row0);
+  } else {  // past the end: a box that is entirely out of range reads zeros
+    r.src = 0;
+    r.seg = 0;
+    r.row0 = ((a.k_seg_len + kChunk - 1) / kChunk) * kChunk;
+    r.valid = 0;
+  }
+  return r;
+}
+
+template <int SLABS, int NSTAGE>
+struct SmemLayout {
+  static constexpr int kQTileBytes = SLABS * kSlabBytes;
+  static constexpr int kStageBytes = SLABS * kSlabBytes;
+  static constexpr int kQOff = 0;
+  static constexpr int kKvOff = 2 * kQTileBytes;
+  static constexpr int kBarOff = kKvOff + NSTAGE * kStageBytes;
+  // barriers: q_full[2], kv_full[NSTAGE], kv_empty[NSTAGE], s_full[2], p_full[2], o_full[2], drain
+  static constexpr int kNumBars = 2 + 2 * NSTAGE + 2 + 2 + 2 + 1;
+  static constexpr int kMiscOff = kBarOff + kNumBars * 8;
+  static constexpr int kTotal = kMiscOff + 16;
+  static constexpr int kDynamic = kTotal + 1024;  // slack to align the base to 1024 bytes
+};
+
+// ---------------------------------------------------------------------------------------------
+// kernel
+// ---------------------------------------------------------------------------------------------
+template <int SLABS, int NSTAGE, bool BF16>
+__global__ void __launch_bounds__(kThreads, 1) attn_fwd_sm100_kernel(const __grid_constant__ Sm100Args a) {
+  using L = SmemLayout<SLABS, NSTAGE>;
+  extern __shared__ unsigned char smem_dyn[];
+  const uint32_t raw = smem_u32(smem_dyn);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  unsigned char* base_ptr = smem_dyn + (base - raw);
+
+  const uint32_t q_smem = base + L::kQOff;
+  const uint32_t kv_smem = base + L::kKvOff;
+  const uint32_t bar0 = base + L::kBarOff;
+  auto bar_q_full = [&](int t) { return bar0 + 8u * t; };
+  auto bar_kv_full = [&](int s) { return bar0 + 8u * (2 + s); };
+  auto bar_kv_empty = [&](int s) { return bar0 + 8u * (2 + NSTAGE + s); };
+  auto bar_s_full = [&](int t) { return bar0 + 8u * (2 + 2 * NSTAGE + t); };
+  auto bar_p_full = [&](int t) { return bar0 + 8u * (4 + 2 * NSTAGE + t); };
+  auto bar_o_full = [&](int t) { return bar0 + 8u * (6 + 2 * NSTAGE + t); };
+  const uint32_t bar_drain = bar0 + 8u * (8 + 2 * NSTAGE);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + L::kMiscOff);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + L::kMiscOff + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int pair = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int n_tiles = a.n_kv_tiles;
+  // query tile t of this CTA covers query chunks 4*pair + 2t and 4*pair + 2t + 1
+  const bool tile_on[2] = {4 * pair < a.q_chunks, 4 * pair + 2 < a.q_chunks};
+
+  if (threadIdx.x == 0) {
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(bar_q_full(t), 1);
+      mbar_init(bar_s_full(t), 1);
+      mbar_init(bar_p_full(t), 128);
+      mbar_init(bar_o_full(t), 1);
+    }
+    for (int s = 0; s < NSTAGE; ++s) {
+      mbar_init(bar_kv_full(s), 1);
+      mbar_init(bar_kv_empty(s), 1);
+    }
+    mbar_init(bar_drain, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 8) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 9) {
+    // ======================= TMA producer =======================
+    if (lane == 0) {
+      int issued = 0;  // ring items armed so far
+      bool ok = true;
+      for (int t = 0; t < 2 && ok; ++t) {
+        if (!tile_on[t]) continue;
+        mbar_arrive_expect_tx(bar_q_full(t), L::kQTileBytes);
+        for (int c = 0; c < 2; ++c) {
+          const int qc = 4 * pair + 2 * t + c;
+          int seg = 0, row0 = ((a.q_seg_len + kChunk - 1) / kChunk) * kChunk;  // out of range -> zeros
+          if (qc < a.q_chunks) {
+            seg = qc / a.q_cps;
+            row0 = (qc - seg * a.q_cps) * kChunk;
+          }
+          for (int s = 0; s < SLABS; ++s)
+            tma_load_5d(q_smem + t * L::kQTileBytes + s * kSlabBytes + c * kBoxBytes, &a.tm_q, bar_q_full(t),
+                        s * 64, row0, seg, h, b);
+        }
+      }
+      const int n_items = 2 * n_tiles;
+      for (int i = 0; i < n_items && ok; ++i) {
+        const int stage = i % NSTAGE;
+        if (i >= NSTAGE) ok = mbar_wait(bar_kv_empty(stage), ((i / NSTAGE) - 1) & 1, abort_flag, 100 + stage);
+        if (!ok) break;
+        mbar_arrive_expect_tx(bar_kv_full(stage), L::kStageBytes);
+        const int j = i >> 1;
+        const bool is_v = i & 1;
+        for (int c = 0; c < 2; ++c) {
+          const ChunkLoc loc = kv_chunk(a, 2 * j + c);
+          const CUtensorMap* tm = loc.src ? (is_v ? &a.tm_v2 : &a.tm_k2) : (is_v ? &a.tm_v : &a.tm_k);
+          for (int s = 0; s < SLABS; ++s)
+            tma_load_5d(kv_smem + stage * L::kStageBytes + s * kSlabBytes + c * kBoxBytes, tm, bar_kv_full(stage),
+                        s * 64, loc.row0, loc.seg, h, b);
+        }
+        issued = i + 1;
+      }
+      if (!ok) {
+        // drain: every armed stage must have received its bytes before the CTA may leave
+        const int first = issued > NSTAGE ? issued - NSTAGE : 0;
+        for (int i = first; i < issued; ++i) {
+          const uint32_t bar = bar_kv_full(i % NSTAGE), par = (i / NSTAGE) & 1;
+          for (int it = 0; it < (1 << 20) && !mbar_try_wait(bar, par); ++it) __nanosleep(64);
+        }
+        for (int t = 0; t < 2; ++t)
+          if (tile_on[t])
+            for (int it = 0; it < (1 << 20) && !mbar_try_wait(bar_q_full(t), 0); ++it) __nanosleep(64);
+      }
+    }
+  } else if (warp == 8) {
+    // ======================= MMA issuer =======================
+    if (lane == 0) {
+      const uint32_t idesc_qk = make_idesc(BF16, false, kTile);
+      const uint32_t idesc_pv = make_idesc(BF16, true, a.dv_n);
+      const int dk16 = a.dk16;
+      const int last_t = tile_on[1] ? 1 : 0;
+      bool ok = true;
+      auto issue_qk = [&](int t, int stage) {
+        const uint32_t qa = q_smem + t * L::kQTileBytes;
+        const uint32_t kb = kv_smem + stage * L::kStageBytes;
+        for (int ks = 0; ks < dk16; ++ks) {
+          const uint32_t off = (ks >> 2) * kSlabBytes + (ks & 3) * 32;
+          tc_mma_ss(tmem_base + t * kTile, desc_kmajor(qa + off), desc_kmajor(kb + off), idesc_qk, ks > 0);
+        }
+      };
+      auto issue_pv = [&](int t, int stage, bool first_tile) {
+        const uint32_t vb = kv_smem + stage * L::kStageBytes;
+        for (int ks = 0; ks < kTile / 16; ++ks)
+          tc_mma_ts(tmem_base + 256 + t * kTile, tmem_base + t * kTile + ks * 8, desc_mnmajor(vb + ks * 2048),
+                    idesc_pv, (!first_tile) || ks > 0);
+      };
+      // prologue: S_t(0) = Q_t K(0)^T
+      ok = mbar_wait(bar_kv_full(0), 0, abort_flag, 200);
+      for (int t = 0; t < 2 && ok; ++t) {
+        if (!tile_on[t]) continue;
+        ok = mbar_wait(bar_q_full(t), 0, abort_flag, 201 + t);
+        if (!ok) break;
+        tc_fence_after();
+        issue_qk(t, 0);
+        tc_commit(bar_s_full(t));
+      }
+      if (ok) tc_commit(bar_kv_empty(0));
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int iv = 2 * j + 1, sv = iv % NSTAGE;
+        const int ik = 2 * j + 2, sk = ik % NSTAGE;
+        const bool more = j + 1 < n_tiles;
+        ok = mbar_wait(bar_kv_full(sv), (iv / NSTAGE) & 1, abort_flag, 210);
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (!tile_on[t]) continue;
+          ok = mbar_wait(bar_p_full(t), j & 1, abort_flag, 220 + t);
+          if (!ok) break;
+          tc_fence_after();
+          issue_pv(t, sv, j == 0);
+          tc_commit(bar_o_full(t));
+          if (t == last_t) tc_commit(bar_kv_empty(sv));  // V(j) is free once both tiles' PV retire
+          if (more) {
+            if (t == 0 || !tile_on[0]) {
+              ok = mbar_wait(bar_kv_full(sk), (ik / NSTAGE) & 1, abort_flag, 230);
+              if (!ok) break;
+              tc_fence_after();
+            }
+            issue_qk(t, sk);
+            tc_commit(bar_s_full(t));
+          }
+        }
+        if (!ok) break;
+        if (more) tc_commit(bar_kv_empty(sk));
+      }
+      if (!ok) {
+        // drain the tensor pipe before TMEM is released
+        tc_commit(bar_drain);
+        for (int it = 0; it < (1 << 20) && !mbar_try_wait(bar_drain, 0); ++it) __nanosleep(64);
+      }
+    }
+  } else {
+    // ======================= softmax + epilogue =======================
+    const int t = warp >> 2;         // query tile of this warp group
+    const int wq = warp & 3;         // TMEM lane quarter this warp may touch
+    const int row = wq * 32 + lane;  // query row inside the tile
+    const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
+    const uint32_t tmem_s = tmem_base + lane_base + t * kTile;
+    const uint32_t tmem_o = tmem_base + lane_base + 256 + t * kTile;
+    bool ok = true;
+    float m_run = -INFINITY;  // running reference maximum, in scaled log2 units
+    float l_run = 0.f;
+    const float sl2 = a.scale_log2;
+    if (tile_on[t]) {
+      for (int j = 0; j < n_tiles; ++j) {
+        ok = __all_sync(0xffffffffu, mbar_wait(bar_s_full(t), j & 1, abort_flag, 300 + t));
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t s[128];
+        XDIT_TMEM_LD32(s, 0, tmem_s + 0);
+        XDIT_TMEM_LD32(s, 32, tmem_s + 32);
+        XDIT_TMEM_LD32(s, 64, tmem_s + 64);
+        XDIT_TMEM_LD32(s, 96, tmem_s + 96);
+        tmem_wait_ld();
+        const int v0 = kv_chunk(a, 2 * j).valid, v1 = kv_chunk(a, 2 * j + 1).valid;
+        if (v0 < kChunk || v1 < kChunk) {
+#pragma unroll
+          for (int c = 0; c < 128; ++c) {
+            const bool dead = (c < 64) ? (c >= v0) : (c - 64 >= v1);
+            if (dead) s[c] = 0xff800000u;  // -inf
+          }
+        }
+        float mx0 = __uint_as_float(s[0]), mx1 = __uint_as_float(s[1]), mx2 = __uint_as_float(s[2]),
+              mx3 = __uint_as_float(s[3]);
+#pragma unroll
+        for (int c = 4; c < 128; c += 4) {
+          mx0 = fmaxf(mx0, __uint_as_float(s[c]));
+          mx1 = fmaxf(mx1, __uint_as_float(s[c + 1]));
+          mx2 = fmaxf(mx2, __uint_as_float(s[c + 2]));
+          mx3 = fmaxf(mx3, __uint_as_float(s[c + 3]));
+        }
+        const float mt = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sl2;
+        if (j == 0) {
+          m_run = mt;
+        } else {
+          // Lazy rescale: keep the old reference maximum unless some row of this warp grew by
+          // more than 2^8; exp2 of at most 8 is safe in fp32 and in the 16-bit P.
+          const bool grow = mt > m_run + 8.f;
+          if (__any_sync(0xffffffffu, grow)) {
+            const float m_new = fmaxf(m_run, mt);
+            const float alpha = ex2(m_run - m_new);
+            ok = __all_sync(0xffffffffu, mbar_wait(bar_o_full(t), (j - 1) & 1, abort_flag, 310 + t));
+            if (!ok) break;
+            tc_fence_after();
+            for (int c0 = 0; c0 < a.dv_n; c0 += 32) {
+              uint32_t o[32];
+              XDIT_TMEM_LD32(o, 0, tmem_o + c0);
+              tmem_wait_ld();
+#pragma unroll
+              for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
+              XDIT_TMEM_ST32(o, 0, tmem_o + c0);
+            }
+            tmem_wait_st();
+            l_run *= alpha;
+            m_run = m_new;
+          }
+        }
+        float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+        uint32_t pk[64];
+#pragma unroll
+        for (int c = 0; c < 128; c += 4) {
+          const float p0 = ex2(fmaf(__uint_as_float(s[c]), sl2, -m_run));
+          const float p1 = ex2(fmaf(__uint_as_float(s[c + 1]), sl2, -m_run));
+          const float p2 = ex2(fmaf(__uint_as_float(s[c + 2]), sl2, -m_run));
+          const float p3 = ex2(fmaf(__uint_as_float(s[c + 3]), sl2, -m_run));
+          sum0 += p0; sum1 += p1; sum2 += p2; sum3 += p3;
+          pk[c / 2] = pack2<BF16>(p0, p1);
+          pk[c / 2 + 1] = pack2<BF16>(p2, p3);
+        }
+        l_run += (sum0 + sum1) + (sum2 + sum3);
+        XDIT_TMEM_ST32(pk, 0, tmem_s + 0);
+        XDIT_TMEM_ST32(pk, 32, tmem_s + 32);
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(bar_p_full(t));
+      }
+      // ---------------- epilogue ----------------
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_o_full(t), (n_tiles - 1) & 1, abort_flag, 320 + t));
+      if (ok) {
+        tc_fence_after();
+        const int qc = 4 * pair + 2 * t + (row >> 6);
+        int seg = 0, trow = 0;
+        bool live = qc < a.q_chunks;
+        if (live) {
+          seg = qc / a.q_cps;
+          trow = (qc - seg * a.q_cps) * kChunk + (row & 63);
+          live = trow < a.q_seg_len;
+        }
+        const int64_t flat = ((int64_t)b * a.H + h) * a.sq_total + (int64_t)seg * a.q_seg_len + trow;
+        const float inv_l = 1.f / l_run;
+        float lse = (m_run + log2f(l_run)) * 0.6931471805599453f;
+        float w = 0.f;
+        const bool merge = a.acc_in != 0;
+        if (merge && live) {
+          const float la = a.lse_acc[flat];
+          if (!(la == -INFINITY && lse == -INFINITY)) {
+            w = 1.f / (1.f + __expf(la - lse));            // sigmoid(lse - la)
+            const float y = la - lse;                        // lse <- la - logsigmoid(la - lse)
+            lse = la - (fminf(y, 0.f) - log1pf(__expf(-fabsf(y))));
+          }
+        }
+        unsigned char* orow = nullptr;
+        if (!a.acc_out)
+          orow = reinterpret_cast<unsigned char*>(a.out) +
+                 2 * (b * a.out_stride_b + h * a.out_stride_h + seg * a.out_stride_seg + trow * a.out_stride_row);
+        float* arow = a.o_acc ? a.o_acc + flat * a.D : nullptr;
+        for (int c0 = 0; c0 < a.dv_n; c0 += 32) {
+          uint32_t o[32];
+          XDIT_TMEM_LD32(o, 0, tmem_o + c0);
+          tmem_wait_ld();
+          if (live) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              const int col = c0 + 8 * g;
+              if (col < a.D) {
+                float v[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(o[8 * g + e]) * inv_l;
+                if (merge) {
+                  const float4 a0 = *reinterpret_cast<const float4*>(arow + col);
+                  const float4 a1 = *reinterpret_cast<const float4*>(arow + col + 4);
+                  const float oa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) v[e] = oa[e] - w * (oa[e] - v[e]);
+                }
+                if (a.acc_out) {
+                  *reinterpret_cast<float4*>(arow + col) = make_float4(v[0], v[1], v[2], v[3]);
+                  *reinterpret_cast<float4*>(arow + col + 4) = make_float4(v[4], v[5], v[6], v[7]);
+                } else {
+                  uint4 pkd;
+                  pkd.x = pack2<BF16>(v[0], v[1]);
+                  pkd.y = pack2<BF16>(v[2], v[3]);
+                  pkd.z = pack2<BF16>(v[4], v[5]);
+                  pkd.w = pack2<BF16>(v[6], v[7]);
+                  *reinterpret_cast<uint4*>(orow + 2 * col) = pkd;
+                }
+              }
+            }
+          }
+        }
+        if (live) {
+          if (a.acc_out) a.lse_acc[flat] = lse;
+          else if (a.lse) a.lse[flat] = lse;
+        }
+      }
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+  }
+  if (threadIdx.x == 0 && *abort_flag && a.status) atomicCAS(a.status, 0, *abort_flag);
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static std::mutex mu;
+  static EncodeTiledFn fn = nullptr;
+  std::lock_guard<std::mutex> lk(mu);
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !p) return nullptr;
+    fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// 5-D map (d, row, segment, head, batch); a TMA box is 64 elements x 64 rows.
+int encode_seq_map(CUtensorMap* tm, const xdit_seq& s, int dtype, int B, int H, int D) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) { set_error("cuTensorMapEncodeTiled is not available from the driver"); return XDIT_E_DRIVER; }
+  const uint64_t es = 2;
+  cuuint64_t dims[5] = {(cuuint64_t)D, (cuuint64_t)s.seg_len, (cuuint64_t)s.nseg, (cuuint64_t)H, (cuuint64_t)B};
+  int64_t st[4] = {s.stride_row, s.stride_seg, s.stride_h, s.stride_b};
+  cuuint64_t strides[4];
+  for (int i = 0; i < 4; ++i) {
+    // a dimension of extent 1 is never stepped; give it a harmless legal stride
+    int64_t v = (dims[i + 1] > 1) ? st[i] : (st[i] > 0 && st[i] % 8 == 0 ? st[i] : (int64_t)((D + 7) / 8 * 8));
+    strides[i] = (cuuint64_t)v * es;
+  }
+  cuuint32_t box[5] = {64, (cuuint32_t)kChunk, 1, 1, 1};
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  CUresult r = fn(tm, dtype == XDIT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5,
+                  const_cast<void*>(s.ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed with CUresult %d (D=%d seg_len=%d nseg=%d strides %lld %lld %lld %lld)",
+              (int)r, D, s.seg_len, s.nseg, (long long)s.stride_row, (long long)s.stride_seg,
+              (long long)s.stride_h, (long long)s.stride_b);
+    return XDIT_E_DRIVER;
+  }
+  return XDIT_OK;
+}
+
+bool seq_ok(const xdit_seq& s, int B, int H, const char* name) {
+  if (((uintptr_t)s.ptr) & 15) { set_error("tcgen05 path: %s pointer is not 16-byte aligned", name); return false; }
+  if (s.stride_row < 0 || (s.seg_len > 1 && s.stride_row % 8)) { set_error("tcgen05 path: %s row stride %lld", name, (long long)s.stride_row); return false; }
+  if (s.nseg > 1 && (s.stride_seg % 8 || s.stride_seg <= 0)) { set_error("tcgen05 path: %s segment stride", name); return false; }
+  if (H > 1 && (s.stride_h % 8 || s.stride_h <= 0)) { set_error("tcgen05 path: %s head stride", name); return false; }
+  if (B > 1 && (s.stride_b % 8 || s.stride_b <= 0)) { set_error("tcgen05 path: %s batch stride", name); return false; }
+  return true;
+}
+
+template <int SLABS, int NSTAGE, bool BF16>
+int launch_inst(const Sm100Args& a, dim3 grid, cudaStream_t stream) {
+  using L = SmemLayout<SLABS, NSTAGE>;
+  static bool configured[16] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 16 || !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd_sm100_kernel<SLABS, NSTAGE, BF16>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
+    if (e != cudaSuccess) return cuda_fail(e, "attn_fwd_sm100 smem attribute");
+    if (dev >= 0 && dev < 16) configured[dev] = true;
+  }
+  attn_fwd_sm100_kernel<SLABS, NSTAGE, BF16><<<grid, kThreads, L::kDynamic, stream>>>(a);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "attn_fwd_sm100_kernel launch");
+  return XDIT_OK;
+}
+
+}  // namespace
+
+int attn_sm100_applicable(const xdit_attn_params& p) {
+  if (p.dtype != XDIT_BF16 && p.dtype != XDIT_F16) { set_error("tcgen05 path: dtype is not bf16/fp16"); return 0; }
+  if (p.D % 8 || p.D < 8 || p.D > 128) { set_error("tcgen05 path: head_dim %d (multiple of 8 up to 128)", p.D); return 0; }
+  if (p.causal) { set_error("tcgen05 path: causal masking is served by the CUDA-core kernel"); return 0; }
+  if (!seq_ok(p.q, p.B, p.H, "q") || !seq_ok(p.k, p.B, p.H, "k") || !seq_ok(p.v, p.B, p.H, "v")) return 0;
+  if (p.k2.ptr && (!seq_ok(p.k2, p.B, p.H, "k2") || !seq_ok(p.v2, p.B, p.H, "v2"))) return 0;
+  if (!p.acc_out) {
+    if (((uintptr_t)p.out) & 15) { set_error("tcgen05 path: out pointer alignment"); return 0; }
+    if (p.out_stride_row % 8 || (p.q.nseg > 1 && p.out_stride_seg % 8) || (p.H > 1 && p.out_stride_h % 8) ||
+        (p.B > 1 && p.out_stride_b % 8)) { set_error("tcgen05 path: out strides"); return 0; }
+  }
+  if ((p.acc_in || p.acc_out) && ((((uintptr_t)p.o_acc) & 15) || (p.D % 4))) { set_error("tcgen05 path: o_acc alignment"); return 0; }
+  return 1;
+}
+
+int launch_attn_sm100(const xdit_attn_params& p, cudaStream_t stream) {
+  Sm100Args a;
+  memset(&a, 0, sizeof(a));
+  int rc;
+  if ((rc = encode_seq_map(&a.tm_q, p.q, p.dtype, p.B, p.H, p.D))) return rc;
+  if ((rc = encode_seq_map(&a.tm_k, p.k, p.dtype, p.B, p.H, p.D))) return rc;
+  if ((rc = encode_seq_map(&a.tm_v, p.v, p.dtype, p.B, p.H, p.D))) return rc;
+  if (p.k2.ptr) {
+    if ((rc = encode_seq_map(&a.tm_k2, p.k2, p.dtype, p.B, p.H, p.D))) return rc;
+    if ((rc = encode_seq_map(&a.tm_v2, p.v2, p.dtype, p.B, p.H, p.D))) return rc;
+  } else {
+    a.tm_k2 = a.tm_k;
+    a.tm_v2 = a.tm_v;
+  }
+  a.q_seg_len = p.q.seg_len;
+  a.q_cps = (p.q.seg_len + kChunk - 1) / kChunk;
+  a.q_chunks = a.q_cps * p.q.nseg;
+  a.k_seg_len = p.k.seg_len;
+  a.k_cps = (p.k.seg_len + kChunk - 1) / kChunk;
+  a.k_chunks_main = a.k_cps * p.k.nseg;
+  a.k2_len = p.k2.ptr ? p.k2.seg_len : 0;
+  a.kv_chunks = a.k_chunks_main + (a.k2_len + kChunk - 1) / kChunk;
+  a.n_kv_tiles = (a.kv_chunks + 1) / 2;
+  a.H = p.H;
+  a.D = p.D;
+  a.dk16 = (p.D + 15) / 16;
+  a.dv_n = a.dk16 * 16;
+  a.sq_total = p.q.nseg * p.q.seg_len;
+  const float scale = p.softmax_scale > 0.f ? p.softmax_scale : 1.0f / sqrtf((float)p.D);
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.out = p.out;
+  a.out_stride_b = p.out_stride_b; a.out_stride_h = p.out_stride_h;
+  a.out_stride_seg = p.out_stride_seg; a.out_stride_row = p.out_stride_row;
+  a.lse = p.lse; a.o_acc = p.o_acc; a.lse_acc = p.lse_acc;
+  a.acc_in = p.acc_in; a.acc_out = p.acc_out;
+  a.status = p.status;
+  dim3 grid((a.q_chunks + 3) / 4, p.H, p.B);
+  const bool bf16 = p.dtype == XDIT_BF16;
+  if (p.D <= 64) {
+    return bf16 ? launch_inst<1, 8, true>(a, grid, stream) : launch_inst<1, 8, false>(a, grid, stream);
+  }
+  return bf16 ? launch_inst<2, 5, true>(a, grid, stream) : launch_inst<2, 5, false>(a, grid, stream);
+}
+
+}  // namespace xdit

@@ -1,0 +1,282 @@
+// extern "C" entry points of libxdit_b200: argument checking and translation of the
+// domain-level parameters (Ulysses peers, joint rows, KV patches) into kernel launches.
+#include <cstdarg>
+#include <cstdio>
+#include <mutex>
+
+#include "common.cuh"
+
+namespace xdit {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+int check_device(int* sm_count) {
+  // Cached per device: the attributes do not change while the process lives.
+  static std::mutex mu;
+  static int cached_dev[16], cached_major[16], cached_sms[16], ncached = 0;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+  int major = -1, sms = 0;
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    for (int i = 0; i < ncached; ++i)
+      if (cached_dev[i] == dev) { major = cached_major[i]; sms = cached_sms[i]; }
+    if (major < 0) {
+      e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+      if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute");
+      e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+      if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute");
+      if (ncached < 16) {
+        cached_dev[ncached] = dev; cached_major[ncached] = major; cached_sms[ncached] = sms;
+        ++ncached;
+      }
+    }
+  }
+  if (major != 10) {
+    set_error("device %d is sm_%d?: this library is built for sm_100a only", dev, major);
+    return XDIT_E_UNSUPPORTED_DEVICE;
+  }
+  if (sm_count) *sm_count = sms;
+  return XDIT_OK;
+}
+
+}  // namespace xdit
+
+using namespace xdit;
+
+extern "C" {
+
+const char* xdit_last_error_string(void) { return g_err; }
+
+int xdit_query_caps(struct xdit_caps* out) {
+  if (!out) { set_error("xdit_query_caps: NULL out"); return XDIT_E_NULL; }
+  out->abi_version = XDIT_ABI_VERSION;
+  out->supported = 0;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+  out->device = dev;
+  cudaDeviceGetAttribute(&out->sm_major, cudaDevAttrComputeCapabilityMajor, dev);
+  cudaDeviceGetAttribute(&out->sm_minor, cudaDevAttrComputeCapabilityMinor, dev);
+  cudaDeviceGetAttribute(&out->sm_count, cudaDevAttrMultiProcessorCount, dev);
+  cudaDeviceGetAttribute(&out->max_smem_per_block, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+  out->supported = (out->sm_major == 10) ? 1 : 0;
+  return XDIT_OK;
+}
+
+int xdit_ulysses_pack(const struct xdit_pack_job* jobs, int32_t njobs, int32_t dtype, int32_t B,
+                      int32_t H, int32_t D, int32_t U, void* stream) {
+  const int es = dtype_size(dtype);
+  if (!es) { set_error("xdit_ulysses_pack: bad dtype %d", dtype); return XDIT_E_DTYPE; }
+  if (!jobs) { set_error("xdit_ulysses_pack: NULL jobs"); return XDIT_E_NULL; }
+  if (njobs < 1 || njobs > XDIT_MAX_PACK_JOBS) {
+    set_error("xdit_ulysses_pack: njobs=%d (1..%d)", njobs, XDIT_MAX_PACK_JOBS);
+    return XDIT_E_SHAPE;
+  }
+  if (B < 1 || H < 1 || D < 1 || U < 1 || H % U != 0) {
+    set_error("xdit_ulysses_pack: B=%d H=%d D=%d U=%d (H must be divisible by U)", B, H, D, U);
+    return XDIT_E_SHAPE;
+  }
+  const int Hl = H / U;
+  RowCopyJob rc[kMaxRowCopyJobs];
+  int n = 0;
+  for (int j = 0; j < njobs; ++j) {
+    const xdit_pack_job& pj = jobs[j];
+    if (pj.s < 0 || pj.s_joint < 0 || pj.s + pj.s_joint == 0) {
+      set_error("xdit_ulysses_pack: job %d has s=%d s_joint=%d", j, pj.s, pj.s_joint);
+      return XDIT_E_SHAPE;
+    }
+    if (!pj.dst || (pj.s && !pj.src) || (pj.s_joint && !pj.joint)) {
+      set_error("xdit_ulysses_pack: NULL pointer in job %d", j);
+      return XDIT_E_NULL;
+    }
+    const int64_t rows = (int64_t)pj.s + pj.s_joint;
+    // destination dims: (peer, head-in-peer, batch, row)
+    const int64_t d_row = (int64_t)D * es;
+    const int64_t d_b = rows * d_row;
+    const int64_t d_h = B * d_b;
+    const int64_t d_p = pj.dst_peer_stride * es;
+    const int main_off = pj.joint_front ? pj.s_joint : 0;
+    const int joint_off = pj.joint_front ? 0 : pj.s;
+    if (pj.s) {
+      RowCopyJob& r = rc[n++];
+      r.src = (const char*)pj.src;
+      r.dst = (char*)pj.dst + main_off * d_row;
+      r.n[0] = U; r.n[1] = Hl; r.n[2] = B; r.n[3] = pj.s;
+      r.s_stride[0] = (int64_t)Hl * pj.src_stride_h * es; r.s_stride[1] = pj.src_stride_h * es;
+      r.s_stride[2] = pj.src_stride_b * es; r.s_stride[3] = pj.src_stride_row * es;
+      r.d_stride[0] = d_p; r.d_stride[1] = d_h; r.d_stride[2] = d_b; r.d_stride[3] = d_row;
+      r.row_bytes = D * es;
+    }
+    if (pj.s_joint) {
+      RowCopyJob& r = rc[n++];
+      r.src = (const char*)pj.joint;
+      r.dst = (char*)pj.dst + joint_off * d_row;
+      r.n[0] = U; r.n[1] = Hl; r.n[2] = B; r.n[3] = pj.s_joint;
+      r.s_stride[0] = (int64_t)Hl * pj.joint_stride_h * es; r.s_stride[1] = pj.joint_stride_h * es;
+      r.s_stride[2] = pj.joint_stride_b * es; r.s_stride[3] = pj.joint_stride_row * es;
+      r.d_stride[0] = d_p; r.d_stride[1] = d_h; r.d_stride[2] = d_b; r.d_stride[3] = d_row;
+      r.row_bytes = D * es;
+    }
+  }
+  return launch_row_copy(rc, n, (cudaStream_t)stream);
+}
+
+int xdit_ulysses_pack_out(const void* src, int64_t stride_b, int64_t stride_h, int64_t stride_row,
+                          void* dst, int32_t dtype, int32_t B, int32_t Hl, int32_t S, int32_t D,
+                          void* stream) {
+  const int es = dtype_size(dtype);
+  if (!es) { set_error("xdit_ulysses_pack_out: bad dtype %d", dtype); return XDIT_E_DTYPE; }
+  if (!src || !dst) { set_error("xdit_ulysses_pack_out: NULL pointer"); return XDIT_E_NULL; }
+  if (B < 1 || Hl < 1 || S < 1 || D < 1) { set_error("xdit_ulysses_pack_out: bad shape"); return XDIT_E_SHAPE; }
+  // dst [S][B][Hl][D]; iterate (1, b, h, row) so that the long axis is innermost
+  RowCopyJob r;
+  r.src = (const char*)src; r.dst = (char*)dst;
+  r.n[0] = 1; r.n[1] = B; r.n[2] = Hl; r.n[3] = S;
+  r.s_stride[0] = 0; r.s_stride[1] = stride_b * es; r.s_stride[2] = stride_h * es; r.s_stride[3] = stride_row * es;
+  const int64_t row = (int64_t)D * es;
+  r.d_stride[0] = 0; r.d_stride[1] = Hl * row; r.d_stride[2] = row; r.d_stride[3] = (int64_t)B * Hl * row;
+  r.row_bytes = D * es;
+  return launch_row_copy(&r, 1, (cudaStream_t)stream);
+}
+
+int xdit_ulysses_unpack_out(const void* recv, void* dst, int32_t dtype, int32_t B, int32_t Hl,
+                            int32_t s, int32_t D, int32_t U, void* stream) {
+  const int es = dtype_size(dtype);
+  if (!es) { set_error("xdit_ulysses_unpack_out: bad dtype %d", dtype); return XDIT_E_DTYPE; }
+  if (!recv || !dst) { set_error("xdit_ulysses_unpack_out: NULL pointer"); return XDIT_E_NULL; }
+  if (B < 1 || Hl < 1 || s < 1 || D < 1 || U < 1) { set_error("xdit_ulysses_unpack_out: bad shape"); return XDIT_E_SHAPE; }
+  // recv [U][s][B][Hl][D] -> dst [B][U][Hl][s][D]; dims (u, b, h, row)
+  const int64_t row = (int64_t)D * es;
+  RowCopyJob r;
+  r.src = (const char*)recv; r.dst = (char*)dst;
+  r.n[0] = U; r.n[1] = B; r.n[2] = Hl; r.n[3] = s;
+  r.s_stride[0] = (int64_t)s * B * Hl * row; r.s_stride[1] = Hl * row; r.s_stride[2] = row;
+  r.s_stride[3] = (int64_t)B * Hl * row;
+  r.d_stride[0] = (int64_t)Hl * s * row; r.d_stride[1] = (int64_t)U * Hl * s * row;
+  r.d_stride[2] = (int64_t)s * row; r.d_stride[3] = row;
+  r.row_bytes = D * es;
+  return launch_row_copy(&r, 1, (cudaStream_t)stream);
+}
+
+int xdit_ulysses_unpack_in(const void* recv, void* dst, int32_t dtype, int32_t B, int32_t Hl,
+                           int32_t s, int32_t D, int32_t U, void* stream) {
+  const int es = dtype_size(dtype);
+  if (!es) { set_error("xdit_ulysses_unpack_in: bad dtype %d", dtype); return XDIT_E_DTYPE; }
+  if (!recv || !dst) { set_error("xdit_ulysses_unpack_in: NULL pointer"); return XDIT_E_NULL; }
+  if (B < 1 || Hl < 1 || s < 1 || D < 1 || U < 1) { set_error("xdit_ulysses_unpack_in: bad shape"); return XDIT_E_SHAPE; }
+  // recv [U][Hl][B][s][D] -> dst [B][Hl][U][s][D]; dims (u, h, b, row)
+  const int64_t row = (int64_t)D * es;
+  RowCopyJob r;
+  r.src = (const char*)recv; r.dst = (char*)dst;
+  r.n[0] = U; r.n[1] = Hl; r.n[2] = B; r.n[3] = s;
+  r.s_stride[0] = (int64_t)Hl * B * s * row; r.s_stride[1] = (int64_t)B * s * row;
+  r.s_stride[2] = (int64_t)s * row; r.s_stride[3] = row;
+  r.d_stride[0] = (int64_t)s * row; r.d_stride[1] = (int64_t)U * s * row;
+  r.d_stride[2] = (int64_t)Hl * U * s * row; r.d_stride[3] = row;
+  r.row_bytes = D * es;
+  return launch_row_copy(&r, 1, (cudaStream_t)stream);
+}
+
+int xdit_kv_patch_update(const struct xdit_kv_patch_params* p, void* stream) {
+  if (!p) { set_error("xdit_kv_patch_update: NULL params"); return XDIT_E_NULL; }
+  const int es = dtype_size(p->dtype);
+  if (!es) { set_error("xdit_kv_patch_update: bad dtype %d", p->dtype); return XDIT_E_DTYPE; }
+  if (!p->k_cache || !p->v_cache || !p->k_new.ptr || !p->v_new.ptr) {
+    set_error("xdit_kv_patch_update: NULL pointer");
+    return XDIT_E_NULL;
+  }
+  if (p->B < 1 || p->H < 1 || p->D < 1 || p->k_new.nseg < 1 || p->k_new.seg_len < 1 ||
+      p->v_new.nseg != p->k_new.nseg || p->v_new.seg_len != p->k_new.seg_len) {
+    set_error("xdit_kv_patch_update: bad shape");
+    return XDIT_E_SHAPE;
+  }
+  const int64_t nrows = (int64_t)p->k_new.nseg * p->k_new.seg_len;
+  if (p->row_start < 0 || p->row_start + nrows > p->cache_rows) {
+    set_error("xdit_kv_patch_update: rows [%d,%lld) outside the cache of %d rows", p->row_start,
+              (long long)(p->row_start + nrows), p->cache_rows);
+    return XDIT_E_SHAPE;
+  }
+  RowCopyJob rc[2];
+  const xdit_seq* srcs[2] = {&p->k_new, &p->v_new};
+  void* dsts[2] = {p->k_cache, p->v_cache};
+  for (int i = 0; i < 2; ++i) {
+    RowCopyJob& r = rc[i];
+    const xdit_seq& s = *srcs[i];
+    r.src = (const char*)s.ptr;
+    r.dst = (char*)dsts[i] + (int64_t)p->row_start * p->cache_stride_row * es;
+    r.n[0] = p->B; r.n[1] = p->H; r.n[2] = s.nseg; r.n[3] = s.seg_len;
+    r.s_stride[0] = s.stride_b * es; r.s_stride[1] = s.stride_h * es;
+    r.s_stride[2] = s.stride_seg * es; r.s_stride[3] = s.stride_row * es;
+    r.d_stride[0] = p->cache_stride_b * es; r.d_stride[1] = p->cache_stride_h * es;
+    r.d_stride[2] = (int64_t)s.seg_len * p->cache_stride_row * es;
+    r.d_stride[3] = p->cache_stride_row * es;
+    r.row_bytes = p->D * es;
+  }
+  return launch_row_copy(rc, 2, (cudaStream_t)stream);
+}
+
+static int attn_check(const struct xdit_attn_params* p) {
+  if (!p) { set_error("xdit_attn_fwd: NULL params"); return XDIT_E_NULL; }
+  if (!dtype_size(p->dtype)) { set_error("xdit_attn_fwd: bad dtype %d", p->dtype); return XDIT_E_DTYPE; }
+  if (p->B < 1 || p->H < 1 || p->D < 1 || p->D > 256) {
+    set_error("xdit_attn_fwd: B=%d H=%d D=%d (D must be 1..256)", p->B, p->H, p->D);
+    return XDIT_E_SHAPE;
+  }
+  if (!p->q.ptr || !p->k.ptr || !p->v.ptr) { set_error("xdit_attn_fwd: NULL q/k/v"); return XDIT_E_NULL; }
+  if (p->q.nseg < 1 || p->q.seg_len < 1 || p->k.nseg < 1 || p->k.seg_len < 1 ||
+      p->v.nseg != p->k.nseg || p->v.seg_len != p->k.seg_len) {
+    set_error("xdit_attn_fwd: bad segment shape (q %dx%d, k %dx%d, v %dx%d)", p->q.nseg,
+              p->q.seg_len, p->k.nseg, p->k.seg_len, p->v.nseg, p->v.seg_len);
+    return XDIT_E_SHAPE;
+  }
+  if ((p->k2.ptr == nullptr) != (p->v2.ptr == nullptr)) {
+    set_error("xdit_attn_fwd: k2 and v2 must be given together");
+    return XDIT_E_NULL;
+  }
+  if (p->k2.ptr && (p->k2.nseg != 1 || p->v2.nseg != 1 || p->k2.seg_len < 1 ||
+                    p->v2.seg_len != p->k2.seg_len)) {
+    set_error("xdit_attn_fwd: joint K/V must be one segment of equal length");
+    return XDIT_E_SHAPE;
+  }
+  if ((p->acc_in || p->acc_out) && (!p->o_acc || !p->lse_acc)) {
+    set_error("xdit_attn_fwd: acc_in/acc_out need o_acc and lse_acc");
+    return XDIT_E_NULL;
+  }
+  if (!p->acc_out && !p->out) { set_error("xdit_attn_fwd: NULL out"); return XDIT_E_NULL; }
+  if (p->causal && (p->q.nseg != 1 || p->k.nseg != 1)) {
+    set_error("xdit_attn_fwd: causal needs single-segment q and k");
+    return XDIT_E_SHAPE;
+  }
+  const int64_t sq = (int64_t)p->q.nseg * p->q.seg_len;
+  const int64_t sk = (int64_t)p->k.nseg * p->k.seg_len + (p->k2.ptr ? p->k2.seg_len : 0);
+  if (sq >= (1ll << 30) || sk >= (1ll << 30)) { set_error("xdit_attn_fwd: sequence too long"); return XDIT_E_SHAPE; }
+  return XDIT_OK;
+}
+
+int xdit_attn_which(const struct xdit_attn_params* p) {
+  int rc = attn_check(p);
+  if (rc) return rc;
+  if (p->force_generic) return 0;
+  return attn_sm100_applicable(*p);
+}
+
+int xdit_attn_fwd(const struct xdit_attn_params* p, void* stream) {
+  int rc = attn_check(p);
+  if (rc) return rc;
+  rc = check_device(nullptr);
+  if (rc) return rc;
+  if (!p->force_generic && attn_sm100_applicable(*p) == 1)
+    return launch_attn_sm100(*p, (cudaStream_t)stream);
+  return launch_attn_generic(*p, (cudaStream_t)stream);
+}
+
+}  // extern "C"

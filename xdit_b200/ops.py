@@ -1,0 +1,265 @@
+"""Tensor-level wrappers over the C-ABI kernels.
+
+Tensors are ``torch`` CUDA tensors used as typed device pointers; all arithmetic happens in
+``libxdit_b200.so``.  A *sequence* argument (q, k, v, fresh KV rows) is either a 4-D view
+``[B, H, S, D]`` or a 5-D view ``[B, H, G, L, D]`` of ``G`` segments of ``L`` rows -- the shape a
+Ulysses all-to-all receive buffer has, one segment per source rank.  Any strides are accepted
+as long as the last axis is contiguous.
+
+There is no CPU implementation: calling these with CPU tensors raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import Optional, Sequence
+
+import torch
+
+from . import _capi
+
+_DTYPES = {torch.bfloat16: _capi.XDIT_BF16, torch.float16: _capi.XDIT_F16, torch.float32: _capi.XDIT_F32}
+_status_bufs: dict = {}
+launch_count = 0  # kernels launched through this module (read by the benchmark)
+
+
+def _require_cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError(
+                "xdit_b200 kernels run on CUDA tensors only (sm_100a); got a tensor on "
+                f"{t.device}. There is no CPU fallback."
+            )
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _dtype(t: torch.Tensor) -> int:
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise TypeError(f"unsupported dtype {t.dtype}") from None
+
+
+def _seq(t: Optional[torch.Tensor]) -> _capi.Seq:
+    s = _capi.Seq()
+    if t is None:
+        return s
+    if t.stride(-1) != 1 and t.shape[-1] != 1:
+        raise ValueError("the head_dim axis must be contiguous")
+    s.ptr = t.data_ptr()
+    if t.dim() == 4:
+        s.stride_b, s.stride_h, s.stride_row = t.stride(0), t.stride(1), t.stride(2)
+        s.stride_seg = 0
+        s.nseg, s.seg_len = 1, t.shape[2]
+    elif t.dim() == 5:
+        s.stride_b, s.stride_h, s.stride_seg, s.stride_row = t.stride(0), t.stride(1), t.stride(2), t.stride(3)
+        s.nseg, s.seg_len = t.shape[2], t.shape[3]
+    else:
+        raise ValueError(f"expected a 4-D or 5-D sequence tensor, got {t.dim()}-D")
+    return s
+
+
+def status_buffer(device) -> torch.Tensor:
+    """Per-device int32 word the attention kernel sets when one of its bounded waits gives up."""
+    device = torch.device(device)
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    buf = _status_bufs.get(key)
+    if buf is None:
+        buf = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", key))
+        _status_bufs[key] = buf
+    return buf
+
+
+def check_status(device=None) -> None:
+    """Synchronise and raise if any attention kernel on ``device`` reported a timed-out wait."""
+    keys = list(_status_bufs) if device is None else [torch.device(device).index or 0]
+    for key in keys:
+        buf = _status_bufs.get(key)
+        if buf is None:
+            continue
+        code = int(buf.item())
+        if code:
+            buf.zero_()
+            raise _capi.XditError(-6, "attention kernel", f"bounded wait gave up (code {code})")
+
+
+def query_caps() -> dict:
+    caps = _capi.Caps()
+    _capi.check(_capi.load().xdit_query_caps(C.byref(caps)), "xdit_query_caps")
+    return {name: getattr(caps, name) for name, _ in caps._fields_}
+
+
+def _attn_params(q, k, v, k2, v2, out, lse, o_acc, lse_acc, acc_in, acc_out, causal, scale, force_generic):
+    p = _capi.AttnParams()
+    p.dtype = _dtype(q)
+    p.B, p.H, p.D = q.shape[0], q.shape[1], q.shape[-1]
+    p.q, p.k, p.v = _seq(q), _seq(k), _seq(v)
+    p.k2, p.v2 = _seq(k2), _seq(v2)
+    if out is not None:
+        p.out = out.data_ptr()
+        so = _seq(out)
+        p.out_stride_b, p.out_stride_h, p.out_stride_seg, p.out_stride_row = (
+            so.stride_b, so.stride_h, so.stride_seg, so.stride_row)
+    p.lse = lse.data_ptr() if lse is not None else None
+    p.o_acc = o_acc.data_ptr() if o_acc is not None else None
+    p.lse_acc = lse_acc.data_ptr() if lse_acc is not None else None
+    p.acc_in, p.acc_out, p.causal = int(bool(acc_in)), int(bool(acc_out)), int(bool(causal))
+    p.softmax_scale = float(scale) if scale else 0.0
+    p.force_generic = int(bool(force_generic))
+    return p
+
+
+def attn_fwd(q, k, v, k2=None, v2=None, *, out=None, lse=None, o_acc=None, lse_acc=None,
+             acc_in=False, acc_out=False, causal=False, scale=None, force_generic=False,
+             want_lse=False):
+    """Dense softmax attention forward (C-ABI ``xdit_attn_fwd``).
+
+    Returns ``(out, lse)``.  ``out`` is allocated like ``q`` (contiguous, same dims) unless given;
+    ``lse`` ([B,H,Sq] fp32) is produced when ``want_lse`` or when a buffer is passed.  With
+    ``acc_out`` the result goes to the fp32 accumulators instead and ``out`` may stay ``None``.
+    """
+    global launch_count
+    _require_cuda(q, k, v, k2, v2, out, lse, o_acc, lse_acc)
+    for t in (k, v, k2, v2):
+        if t is not None and t.dtype != q.dtype:
+            raise TypeError("q, k, v (and joint k, v) must share one dtype")
+    sq = q.shape[2] if q.dim() == 4 else q.shape[2] * q.shape[3]
+    if out is None and not acc_out:
+        out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+    if lse is None and want_lse and not acc_out:
+        lse = torch.empty(q.shape[0], q.shape[1], sq, dtype=torch.float32, device=q.device)
+    p = _attn_params(q, k, v, k2, v2, out, lse, o_acc, lse_acc, acc_in, acc_out, causal, scale, force_generic)
+    p.status = status_buffer(q.device).data_ptr()
+    with torch.cuda.device(q.device):
+        _capi.check(_capi.load().xdit_attn_fwd(C.byref(p), _stream(q)), "xdit_attn_fwd")
+    launch_count += 1
+    return out, lse
+
+
+def attn_which(q, k, v, k2=None, v2=None, *, out=None, causal=False, acc=False) -> int:
+    """1 when the tcgen05 kernel would serve this call, 0 for the CUDA-core kernel."""
+    dummy = q if out is None else out
+    acc_buf = q if acc else None
+    p = _attn_params(q, k, v, k2, v2, dummy, None, acc_buf, acc_buf, acc, False, causal, None, False)
+    return _capi.load().xdit_attn_which(C.byref(p))
+
+
+def ulysses_pack(items: Sequence[dict], U: int) -> None:
+    """Pack up to four tensors into all-to-all send buffers with one launch (``xdit_ulysses_pack``).
+
+    Each item: ``src`` [B,H,s,D]; optional ``joint`` [B,H,sj,D] and ``front`` (bool); ``dst`` a
+    1-D tensor positioned at this tensor's slot inside peer 0's block; ``peer_stride`` the
+    distance in elements between two peers' blocks of that buffer.
+    """
+    global launch_count
+    n = len(items)
+    if not 1 <= n <= _capi.XDIT_MAX_PACK_JOBS:
+        raise ValueError(f"1..{_capi.XDIT_MAX_PACK_JOBS} tensors per pack call")
+    jobs = (_capi.PackJob * n)()
+    ref = items[0]["src"]
+    B, H, _, D = ref.shape
+    for j, it in zip(jobs, items):
+        src, joint, dst = it["src"], it.get("joint"), it["dst"]
+        _require_cuda(src, joint, dst)
+        if src.dtype != ref.dtype or src.shape[0] != B or src.shape[1] != H or src.shape[3] != D:
+            raise ValueError("tensors packed together must agree in dtype, B, H and D")
+        if src.stride(3) != 1 and D != 1:
+            raise ValueError("the head_dim axis must be contiguous")
+        j.src = src.data_ptr()
+        j.src_stride_b, j.src_stride_h, j.src_stride_row = src.stride(0), src.stride(1), src.stride(2)
+        j.s = src.shape[2]
+        if joint is not None:
+            if joint.stride(3) != 1 and D != 1:
+                raise ValueError("the head_dim axis must be contiguous")
+            j.joint = joint.data_ptr()
+            j.joint_stride_b, j.joint_stride_h, j.joint_stride_row = joint.stride(0), joint.stride(1), joint.stride(2)
+            j.s_joint = joint.shape[2]
+            j.joint_front = int(bool(it.get("front", False)))
+        j.dst = dst.data_ptr()
+        j.dst_peer_stride = int(it["peer_stride"])
+    with torch.cuda.device(ref.device):
+        _capi.check(_capi.load().xdit_ulysses_pack(jobs, n, _dtype(ref), B, H, D, U, _stream(ref)),
+                    "xdit_ulysses_pack")
+    launch_count += 1
+
+
+def ulysses_pack_out(x: torch.Tensor) -> torch.Tensor:
+    """[B,Hl,S,D] -> [S,B,Hl,D] contiguous (the reference's output-side wire layout)."""
+    global launch_count
+    _require_cuda(x)
+    B, Hl, S, D = x.shape
+    dst = torch.empty(S, B, Hl, D, dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        _capi.check(_capi.load().xdit_ulysses_pack_out(x.data_ptr(), x.stride(0), x.stride(1), x.stride(2),
+                                                       dst.data_ptr(), _dtype(x), B, Hl, S, D, _stream(x)),
+                    "xdit_ulysses_pack_out")
+    launch_count += 1
+    return dst
+
+
+def ulysses_unpack_out(recv: torch.Tensor, B: int, Hl: int, s: int, D: int, U: int) -> torch.Tensor:
+    """recv [U][s][B][Hl][D] -> [B, U*Hl, s, D] contiguous."""
+    global launch_count
+    _require_cuda(recv)
+    dst = torch.empty(B, U * Hl, s, D, dtype=recv.dtype, device=recv.device)
+    with torch.cuda.device(recv.device):
+        _capi.check(_capi.load().xdit_ulysses_unpack_out(recv.data_ptr(), dst.data_ptr(), _dtype(recv), B, Hl, s,
+                                                         D, U, _stream(recv)), "xdit_ulysses_unpack_out")
+    launch_count += 1
+    return dst
+
+
+def ulysses_unpack_in(recv: torch.Tensor, B: int, Hl: int, s: int, D: int, U: int) -> torch.Tensor:
+    """recv [U][Hl][B][s][D] -> [B, Hl, U*s, D] contiguous."""
+    global launch_count
+    _require_cuda(recv)
+    dst = torch.empty(B, Hl, U * s, D, dtype=recv.dtype, device=recv.device)
+    with torch.cuda.device(recv.device):
+        _capi.check(_capi.load().xdit_ulysses_unpack_in(recv.data_ptr(), dst.data_ptr(), _dtype(recv), B, Hl, s,
+                                                        D, U, _stream(recv)), "xdit_ulysses_unpack_in")
+    launch_count += 1
+    return dst
+
+
+def kv_patch_update(k_cache: torch.Tensor, v_cache: torch.Tensor, k_new: torch.Tensor,
+                    v_new: torch.Tensor, row_start: int) -> None:
+    """Overwrite cache rows [row_start, row_start + n) of [B,H,S,D] caches (``xdit_kv_patch_update``)."""
+    global launch_count
+    _require_cuda(k_cache, v_cache, k_new, v_new)
+    if k_cache.stride() != v_cache.stride() or k_cache.shape != v_cache.shape:
+        raise ValueError("K and V caches must share shape and strides")
+    p = _capi.KvPatchParams()
+    p.dtype = _dtype(k_cache)
+    p.B, p.H, p.D = k_cache.shape[0], k_cache.shape[1], k_cache.shape[3]
+    p.k_cache, p.v_cache = k_cache.data_ptr(), v_cache.data_ptr()
+    p.cache_stride_b, p.cache_stride_h, p.cache_stride_row = k_cache.stride(0), k_cache.stride(1), k_cache.stride(2)
+    p.cache_rows = k_cache.shape[2]
+    p.k_new, p.v_new = _seq(k_new), _seq(v_new)
+    p.row_start = int(row_start)
+    with torch.cuda.device(k_cache.device):
+        _capi.check(_capi.load().xdit_kv_patch_update(C.byref(p), _stream(k_cache)), "xdit_kv_patch_update")
+    launch_count += 1
+
+
+def merge_out_lse(o_acc: torch.Tensor, lse_acc: torch.Tensor, out_b: torch.Tensor, lse_b: torch.Tensor,
+                  first: bool, out_final: Optional[torch.Tensor] = None) -> None:
+    """In-place online-softmax merge of (out_b, lse_b) into fp32 (o_acc, lse_acc)."""
+    global launch_count
+    _require_cuda(o_acc, lse_acc, out_b, lse_b, out_final)
+    if not (o_acc.is_contiguous() and lse_acc.is_contiguous() and out_b.is_contiguous() and lse_b.is_contiguous()):
+        raise ValueError("merge_out_lse needs contiguous tensors")
+    D = out_b.shape[-1]
+    rows = out_b.numel() // D
+    with torch.cuda.device(o_acc.device):
+        _capi.check(_capi.load().xdit_merge_out_lse(
+            o_acc.data_ptr(), lse_acc.data_ptr(), out_b.data_ptr(), lse_b.data_ptr(),
+            out_final.data_ptr() if out_final is not None else None, _dtype(out_b), rows, D, int(bool(first)),
+            _stream(o_acc)), "xdit_merge_out_lse")
+    launch_count += 1
+
+
+def default_scale(D: int) -> float:
+    return 1.0 / math.sqrt(D)
