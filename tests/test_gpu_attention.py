@@ -1,0 +1,247 @@
+"""Attention kernels through the C ABI on a B200 against the oracle.
+
+Tolerances (bf16/fp16): max-abs <= 2e-2 and cosine >= 0.9999 versus the oracle evaluated in
+float64 on the same rounded inputs; fp32 (CUDA-core kernel): max-abs <= 2e-5.  LSE: 2e-3."""
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from oracle import usp_oracle as O  # noqa: E402
+from tests.gpu_util import compare, np64, oracle_attn, rand  # noqa: E402
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from xdit_b200 import build, ops
+
+    build.build()
+    assert ops.query_caps()["supported"] == 1
+    return ops
+
+
+def _run(ops, q, k, v, k2=None, v2=None, **kw):
+    out, lse = ops.attn_fwd(q, k, v, k2, v2, want_lse=True, **kw)
+    torch.cuda.synchronize()
+    ops.check_status()
+    return out, lse
+
+
+# ------------------------------------------------------------------ CUDA-core kernel
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,H,Sq,Sk,D,causal", [
+    (1, 2, 50, 50, 32, False), (2, 3, 33, 130, 4, False), (1, 2, 128, 128, 32, True),
+    (1, 1, 1, 1, 8, False), (1, 2, 70, 200, 160, False), (1, 1, 97, 97, 72, True),
+])
+def test_generic_kernel(ops, dtype, B, H, Sq, Sk, D, causal):
+    q, k, v = rand((B, H, Sq, D), dtype, 1), rand((B, H, Sk, D), dtype, 2), rand((B, H, Sk, D), dtype, 3)
+    out, lse = _run(ops, q, k, v, causal=causal, force_generic=True)
+    want, want_lse = oracle_attn(q, k, v, causal=causal)
+    if dtype == torch.float32:
+        compare(out, want, "out", max_abs=2e-5)
+        compare(lse, want_lse, "lse", max_abs=2e-5, cos=0.0)
+    else:
+        compare(out, want, "out")
+        compare(lse, want_lse, "lse", max_abs=2e-3, cos=0.0)
+
+
+def test_generic_config1_fp32_joint(ops):
+    """BASELINE config 1 as one dense call: 24 heads x 128, 4096 image + 512 joint keys, fp32; a
+    4-head slice keeps the float64 oracle in seconds."""
+    B, H, S, Sj, D = 1, 4, 4096, 512, 128
+    q = rand((B, H, 600, D), torch.float32, 0)
+    k, v = rand((B, H, S, D), torch.float32, 1), rand((B, H, S, D), torch.float32, 2)
+    jk, jv = rand((B, H, Sj, D), torch.float32, 3), rand((B, H, Sj, D), torch.float32, 4)
+    assert ops.attn_which(q, k, v, jk, jv) == 0
+    out, lse = _run(ops, q, k, v, jk, jv)
+    want, want_lse = oracle_attn(q, k, v, jk, jv)
+    compare(out, want, "out", max_abs=2e-5)
+    compare(lse, want_lse, "lse", max_abs=2e-5, cos=0.0)
+
+
+# ------------------------------------------------------------------ tcgen05 kernel
+SM100_SHAPES = [
+    # B, H, Sq, Sk, D
+    (1, 2, 256, 256, 128),      # exact tiles
+    (1, 2, 128, 128, 128),      # one query tile, second tile of the CTA idle
+    (2, 3, 300, 333, 128),      # ragged on both sides, batch > 1
+    (1, 2, 64, 1, 128),         # a single key
+    (1, 1, 1, 577, 128),        # a single query
+    (1, 4, 515, 1200, 64),      # one-slab head_dim
+    (1, 2, 200, 300, 72),       # PixArt head_dim: K padded to 80, V N = 80
+    (1, 2, 128, 257, 32),       # head_dim of the reference's ring test
+    (1, 2, 130, 190, 8),        # smallest head_dim of the TMA path
+    (1, 3, 1030, 2050, 128),    # several CTAs per head, 17 key tiles
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,H,Sq,Sk,D", SM100_SHAPES)
+def test_sm100_kernel(ops, dtype, B, H, Sq, Sk, D):
+    q, k, v = rand((B, H, Sq, D), dtype, 1), rand((B, H, Sk, D), dtype, 2), rand((B, H, Sk, D), dtype, 3)
+    assert ops.attn_which(q, k, v) == 1
+    out, lse = _run(ops, q, k, v)
+    want, want_lse = oracle_attn(q, k, v)
+    compare(lse, want_lse, "lse", max_abs=2e-3, cos=0.0)
+    compare(out, want, "out")
+
+
+def test_sm100_matches_generic_kernel(ops):
+    q, k, v = (rand((1, 2, 333, 128), torch.bfloat16, i) for i in range(3))
+    a, la = _run(ops, q, k, v)
+    b, lb = _run(ops, q, k, v, force_generic=True)
+    compare(a, np64(b), "tcgen05 vs CUDA-core", max_abs=1e-2)
+    compare(la, np64(lb), "lse", max_abs=2e-3, cos=0.0)
+
+
+def test_sm100_strided_views(ops):
+    """[B,S,H,D] memory viewed as [B,H,S,D], as the processors pass it (transformer_flux.py:170-172)."""
+    B, H, S, D = 2, 4, 300, 128
+    q, k, v = (rand((B, S, H, D), torch.bfloat16, i).transpose(1, 2) for i in range(3))
+    assert ops.attn_which(q, k, v) == 1
+    out = torch.empty(B, S, H, D, dtype=torch.bfloat16, device="cuda").transpose(1, 2)
+    _run(ops, q, k, v, out=out)
+    compare(out, oracle_attn(q, k, v)[0], "out")
+
+
+@pytest.mark.parametrize("D", [128, 64, 72])
+def test_sm100_joint_second_source(ops, D):
+    """Joint (text) K/V as a second source == torch.cat of usp.py:239-241, without the copy."""
+    B, H, Sq, Sk, Sj = 1, 3, 260, 450, 77
+    q, k, v = rand((B, H, Sq, D), torch.bfloat16, 1), rand((B, H, Sk, D), torch.bfloat16, 2), rand((B, H, Sk, D), torch.bfloat16, 3)
+    jk_full, jv_full = rand((B, 2 * H, Sj, D), torch.bfloat16, 4), rand((B, 2 * H, Sj, D), torch.bfloat16, 5)
+    jk, jv = jk_full[:, H:], jv_full[:, H:]  # head slice of a replicated tensor: a strided view
+    out, lse = _run(ops, q, k, v, jk, jv)
+    want, want_lse = oracle_attn(q, k, v, jk, jv)
+    compare(lse, want_lse, "lse", max_abs=2e-3, cos=0.0)
+    compare(out, want, "out")
+
+
+@pytest.mark.parametrize("G,L", [(2, 576), (8, 72), (3, 100), (4, 64)])
+def test_sm100_segmented_sequences(ops, G, L):
+    """q/k/v as G segments (the receive buffer of a Ulysses all-to-all): equals attention over
+    the concatenated rows, output written with the same segmentation."""
+    B, H, D = 1, 2, 128
+    def seg(seed, extra=0):
+        buf = rand((G, H, B, L + extra, D), torch.bfloat16, seed)  # [peer][head][batch][rows][D]
+        return buf.permute(2, 1, 0, 3, 4)[:, :, :, :L]
+    q, k, v = seg(1), seg(2, 5), seg(3, 5)
+    out_buf = torch.zeros(G, H, B, L, D, dtype=torch.bfloat16, device="cuda")
+    out = out_buf.permute(2, 1, 0, 3, 4)
+    assert ops.attn_which(q, k, v, out=out) == 1
+    _, lse = _run(ops, q, k, v, out=out)
+    want, want_lse = oracle_attn(q, k, v)
+    compare(lse, want_lse, "lse", max_abs=2e-3, cos=0.0)
+    compare(out.reshape(B, H, G * L, D), want, "out")
+
+
+@pytest.mark.parametrize("force_generic", [False, True])
+def test_ring_merge_in_epilogue(ops, force_generic):
+    """Three key shards visited with acc_in/acc_out == one dense call (ring steps, usp.py:46-74)."""
+    B, H, Sq, D = 1, 2, 300, 128
+    q = rand((B, H, Sq, D), torch.bfloat16, 0)
+    ks = [rand((B, H, n, D), torch.bfloat16, 10 + i) for i, n in enumerate((200, 333, 128))]
+    vs = [rand((B, H, n, D), torch.bfloat16, 20 + i) for i, n in enumerate((200, 333, 128))]
+    jk, jv = rand((B, H, 40, D), torch.bfloat16, 30), rand((B, H, 40, D), torch.bfloat16, 31)
+    o_acc = torch.empty(B, H, Sq, D, dtype=torch.float32, device="cuda")
+    lse_acc = torch.empty(B, H, Sq, dtype=torch.float32, device="cuda")
+    out = torch.empty_like(q)
+    lse = torch.empty(B, H, Sq, dtype=torch.float32, device="cuda")
+    for i in range(3):
+        last = i == 2
+        ops.attn_fwd(q, ks[i], vs[i], jk if last else None, jv if last else None, out=out if last else None,
+                     lse=lse if last else None, o_acc=o_acc, lse_acc=lse_acc, acc_in=i > 0, acc_out=not last,
+                     force_generic=force_generic)
+    torch.cuda.synchronize()
+    ops.check_status()
+    want, want_lse = oracle_attn(q, torch.cat(ks + [jk], 2), torch.cat(vs + [jv], 2))
+    compare(lse, want_lse, "lse", max_abs=2e-3, cos=0.0)
+    compare(out, want, "out")
+
+
+def test_large_magnitude_rows_rescale(ops):
+    """Keys whose scores grow along the sequence force the lazy rescale path (max grows by > 2^8)."""
+    B, H, Sq, Sk, D = 1, 1, 128, 1024, 128
+    q = rand((B, H, Sq, D), torch.bfloat16, 0)
+    k = rand((B, H, Sk, D), torch.bfloat16, 1)
+    ramp = torch.linspace(0.2, 6.0, Sk, device="cuda").view(1, 1, Sk, 1)
+    k = (k.float() * ramp).to(torch.bfloat16)
+    v = rand((B, H, Sk, D), torch.bfloat16, 2)
+    out, lse = _run(ops, q, k, v)
+    want, want_lse = oracle_attn(q, k, v)
+    compare(lse, want_lse, "lse", max_abs=5e-3, cos=0.0)
+    compare(out, want, "out")
+
+
+# ------------------------------------------------------------------ USP on one rank vs the reference fixture
+def test_usp_single_rank_golden(ops):
+    import xdit_b200
+
+    xdit_b200.init_sequence_parallel(1, 1)
+    z = np.load(os.path.join(HERE, "golden", "usp_u1r1_rear.npz"))
+    q, k, v, jq, jk, jv = (torch.from_numpy(z[n]).cuda() for n in ("q", "k", "v", "jq", "jk", "jv"))
+    out = xdit_b200.USP(q, k, v, joint_query=jq, joint_key=jk, joint_value=jv, joint_strategy="rear")
+    torch.cuda.synchronize()
+    compare(out, z["out"][0], "fp32 USP vs reference", max_abs=2e-5)
+    b = lambda t: t.to(torch.bfloat16)
+    out = xdit_b200.USP(b(q), b(k), b(v), joint_query=b(jq), joint_key=b(jk), joint_value=b(jv), joint_strategy="rear")
+    torch.cuda.synchronize()
+    ops.check_status()
+    compare(out, z["out"][0], "bf16 USP vs reference (fp32 inputs rounded)", max_abs=3e-2, cos=0.999)
+
+
+def test_usp_errors(ops):
+    import xdit_b200
+    from xdit_b200.attention_backend import AttentionBackendType
+
+    q = rand((1, 2, 16, 64), torch.bfloat16, 0)
+    with pytest.raises(ValueError, match="Invalid joint_strategy"):
+        xdit_b200.USP(q, q, q, joint_query=q, joint_key=q, joint_value=q, joint_strategy="middle")
+    with pytest.raises(NotImplementedError, match="not registered"):
+        xdit_b200.USP(q, q, q, backend=AttentionBackendType.AITER_FP8)
+    with pytest.raises(NotImplementedError, match="masked"):
+        xdit_b200.USP(q, q, q, attention_kwargs={"attn_mask": torch.ones(16, 16, device="cuda")})
+
+
+# ------------------------------------------------------------------ full-size properties
+def test_flux_shape_split_merge_property(ops):
+    """Flux.1-dev attention shape (24 x 128, 4608 tokens): attention over all keys equals the fp32
+    merge of attention over two key halves; and it is invariant to a permutation of the keys."""
+    B, H, S, D = 1, 24, 4608, 128
+    q, k, v = (rand((B, H, S, D), torch.bfloat16, i) for i in range(3))
+    full, lse_full = _run(ops, q, k, v)
+    o_acc = torch.empty(B, H, S, D, dtype=torch.float32, device="cuda")
+    lse_acc = torch.empty(B, H, S, dtype=torch.float32, device="cuda")
+    half = torch.empty_like(q)
+    lse_half = torch.empty_like(lse_full)
+    ops.attn_fwd(q, k[:, :, :2000], v[:, :, :2000], o_acc=o_acc, lse_acc=lse_acc, acc_out=True)
+    ops.attn_fwd(q, k[:, :, 2000:], v[:, :, 2000:], out=half, lse=lse_half, o_acc=o_acc, lse_acc=lse_acc, acc_in=True)
+    perm = torch.randperm(S, generator=torch.Generator().manual_seed(0)).cuda()
+    permuted, _ = _run(ops, q, k[:, :, perm].contiguous(), v[:, :, perm].contiguous())
+    torch.cuda.synchronize()
+    ops.check_status()
+    compare(half, np64(full), "split+merge vs full", max_abs=1e-2)
+    compare(lse_half, np64(lse_full), "lse", max_abs=1e-3, cos=0.0)
+    compare(permuted, np64(full), "key permutation", max_abs=1e-2)
+    # one head against the oracle
+    want, _ = oracle_attn(q[:, :1], k[:, :1], v[:, :1])
+    compare(full[:, :1], want, "head 0 vs oracle")
+
+
+def test_reference_test_shape_14867(ops):
+    """tests/layers/usp_test.py:36: (1,24,14867,128) bf16, tolerance there 0.05 against sdpa_flash;
+    here 4 heads against the oracle at the tolerance of this suite."""
+    B, H, S, D = 1, 24, 14867, 128
+    q, k, v = (rand((B, H, S, D), torch.bfloat16, i) for i in range(3))
+    out, _ = _run(ops, q, k, v)
+    for h in (0, 23):
+        want, _ = oracle_attn(q[:, h:h + 1, :2048], k[:, h:h + 1], v[:, h:h + 1])
+        compare(out[:, h:h + 1, :2048], want, f"head {h}")
+    want, _ = oracle_attn(q[:, 5:6, -1500:], k[:, 5:6], v[:, 5:6])
+    compare(out[:, 5:6, -1500:], want, "tail rows")

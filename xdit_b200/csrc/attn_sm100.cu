@@ -59,6 +59,9 @@ struct alignas(64) Sm100Args {
   float* lse_acc;
   int32_t acc_in, acc_out;
   int32_t* status;
+#ifdef XDIT_DEBUG_DUMP
+  float* dbg_s;  // [2][128][128] raw S of key tile 0 of CTA (0,0,0), then [2][128][128] raw O
+#endif
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -421,6 +424,11 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_sm100_kernel(const __gri
         XDIT_TMEM_LD32(s, 64, tmem_s + 64);
         XDIT_TMEM_LD32(s, 96, tmem_s + 96);
         tmem_wait_ld();
+#ifdef XDIT_DEBUG_DUMP
+        if (a.dbg_s && j == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+          for (int c = 0; c < 128; ++c) a.dbg_s[(t * 128 + row) * 128 + c] = __uint_as_float(s[c]);
+        }
+#endif
         const int v0 = kv_chunk(a, 2 * j).valid, v1 = kv_chunk(a, 2 * j + 1).valid;
         if (v0 < kChunk || v1 < kChunk) {
 #pragma unroll
@@ -517,6 +525,13 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_sm100_kernel(const __gri
           uint32_t o[32];
           XDIT_TMEM_LD32(o, 0, tmem_o + c0);
           tmem_wait_ld();
+#ifdef XDIT_DEBUG_DUMP
+          if (a.dbg_s && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+            for (int c = 0; c < 32; ++c)
+              a.dbg_s[2 * 128 * 128 + (t * 128 + row) * 128 + c0 + c] = __uint_as_float(o[c]);
+            if (c0 == 0) a.dbg_s[4 * 128 * 128 + t * 128 + row] = l_run;
+          }
+#endif
           if (live) {
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
@@ -693,6 +708,10 @@ int launch_attn_sm100(const xdit_attn_params& p, cudaStream_t stream) {
   a.lse = p.lse; a.o_acc = p.o_acc; a.lse_acc = p.lse_acc;
   a.acc_in = p.acc_in; a.acc_out = p.acc_out;
   a.status = p.status;
+#ifdef XDIT_DEBUG_DUMP
+  extern float* g_xdit_dbg_s;
+  a.dbg_s = g_xdit_dbg_s;
+#endif
   dim3 grid((a.q_chunks + 3) / 4, p.H, p.B);
   const bool bf16 = p.dtype == XDIT_BF16;
   if (p.D <= 64) {
@@ -701,4 +720,12 @@ int launch_attn_sm100(const xdit_attn_params& p, cudaStream_t stream) {
   return bf16 ? launch_inst<2, 5, true>(a, grid, stream) : launch_inst<2, 5, false>(a, grid, stream);
 }
 
+#ifdef XDIT_DEBUG_DUMP
+float* g_xdit_dbg_s = nullptr;
+#endif
+
 }  // namespace xdit
+
+#ifdef XDIT_DEBUG_DUMP
+extern "C" XDIT_API void xdit_debug_set_dump(float* p) { xdit::g_xdit_dbg_s = p; }
+#endif
