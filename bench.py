@@ -115,20 +115,19 @@ def run_reference(args, w, name):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    import numpy as np
+    import torch
 
     from oracle import usp_oracle as O
 
     cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
     S, D = w["S"], w["D"]
-    if name == "wan":
-        S = 9450  # one Ulysses/ring shard length: the full 75.6K x 75.6K score matrix does not fit a host step
-    rng = np.random.default_rng(0)
+    g = torch.Generator().manual_seed(0)
 
     def one(heads):
-        q, k, v = (rng.standard_normal((1, heads, S, D), dtype=np.float32) for _ in range(3))
+        q, k, v = (torch.randn(1, heads, S, D, generator=g) for _ in range(3))
         t0 = time.perf_counter()
-        O.attention_dense(q, k, v, dtype=np.float32)
+        O.attention_dense_torch_cpu(q, k, v)
         return time.perf_counter() - t0
 
     t_head = one(1)
@@ -141,7 +140,8 @@ def run_reference(args, w, name):
         total += one(heads)
     fl = 4.0 * S * S * heads * D
     val = fl * args.steps / total / 1e12
-    sample = f"{heads} of {w['H']} heads of one layer, {S} tokens, fp32 numpy/BLAS, per step"
+    sample = (f"{heads} of {w['H']} heads of one layer, {S} tokens, fp32 torch CPU SDPA "
+              f"(the reference's SDPA back-end body) on {cores} threads, per step")
     line = {
         "impl": "reference", "metric": "usp_attn_tflops", "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": total / args.steps * 1e3,
@@ -163,18 +163,15 @@ def make_layer_inputs(torch, w, P, rank, layers, device, pinned=False):
     S, H, D = w["S"], w["H"], w["D"]
     s = S // P
     out = []
+    gg = torch.Generator(device=device)
     for layer in range(layers):
-        g = torch.Generator().manual_seed(1000 + layer)
         qkv = []
-        for _ in range(3):
-            # draw only this rank's shard, deterministically: seed advanced per (layer, tensor)
-            full_seed = int(torch.randint(0, 2**31 - 1, (1,), generator=g))
-            gg = torch.Generator().manual_seed(full_seed + rank)
-            t = torch.randn(1, H, s, D, generator=gg, dtype=torch.float32).to(torch.bfloat16)
+        for i in range(3):
+            # N(0,1) drawn on the device from a seed per (layer, tensor, rank); host sets are copies
+            gg.manual_seed(1000003 * (layer + 1) + 1009 * i + rank)
+            t = torch.randn(1, H, s, D, generator=gg, dtype=torch.float32, device=device).to(torch.bfloat16)
             if pinned:
-                t = t.pin_memory()
-            else:
-                t = t.to(device)
+                t = t.cpu().pin_memory()
             qkv.append(t)
         out.append(tuple(qkv))
     return out
@@ -253,26 +250,85 @@ def run_workload(torch, dist, xdit_b200, ops, name, w, args, device, rank, world
     return res
 
 
+def hbm_kernels(torch, ops, device, hbm_peak, peak_kind):
+    """Achieved HBM GB/s (algorithmic bytes = read + write of the moved rows) of the HBM-bound
+    kernels at the shapes of the configs, CUDA events, 512 MB written between repeats to flush L2."""
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device=device)
+
+    def timeit(fn, reps=10):
+        ts = []
+        for _ in range(3):
+            fn()
+        for _ in range(reps):
+            flush.fill_(1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); fn(); e1.record()
+            torch.cuda.synchronize(device)
+            ts.append(e0.elapsed_time(e1))
+        ts.sort()
+        return ts[len(ts) // 2] * 1e-3
+
+    res = {}
+    bf = torch.bfloat16
+    # Ulysses pack of Wan q,k,v at R4xU2: three [1,40,9450,128] tensors viewed from [1,9450,40,128]
+    H, s, D, U = 40, 9450, 128, 2
+    srcs = [torch.randn(1, s, H, D, device=device, dtype=bf).transpose(1, 2) for _ in range(3)]
+    blk = (H // U) * s * D
+    send = torch.empty(3 * U * blk, dtype=bf, device=device)
+    items = [dict(src=t, dst=send[i * blk:], peer_stride=3 * blk) for i, t in enumerate(srcs)]
+    t = timeit(lambda: ops.ulysses_pack(items, U))
+    nbytes = 2 * 3 * H * s * D * 2
+    res["ulysses_pack_wan_qkv"] = {"bytes": nbytes, "ms": t * 1e3, "achieved": nbytes / t / 1e9}
+    del srcs, send
+    # PipeFusion stale-KV patch, PixArt-Sigma 2048^2: 2048 fresh rows of 16 x 72 into 16384-row caches
+    kc = torch.zeros(1, 16, 16384, 72, dtype=bf, device=device)
+    vc = torch.zeros_like(kc)
+    kn = torch.randn(1, 2048, 16, 72, device=device, dtype=bf).transpose(1, 2)
+    vn = torch.randn(1, 2048, 16, 72, device=device, dtype=bf).transpose(1, 2)
+    t = timeit(lambda: ops.kv_patch_update(kc, vc, kn, vn, 4096))
+    nbytes = 2 * 2 * 16 * 2048 * 72 * 2
+    res["kv_patch_pixart"] = {"bytes": nbytes, "ms": t * 1e3, "achieved": nbytes / t / 1e9}
+    # stand-alone merge at one Wan ring step: rows = 20 heads x 18900, D = 128
+    rows = 20 * 18900
+    oa = torch.randn(rows, 128, device=device)
+    la = torch.randn(rows, device=device)
+    ob = torch.randn(rows, 128, device=device, dtype=bf)
+    lb = torch.randn(rows, device=device)
+    t = timeit(lambda: ops.merge_out_lse(oa, la, ob, lb, first=False))
+    nbytes = rows * 128 * (4 + 4 + 2) + rows * 12
+    res["merge_wan_ring_step"] = {"bytes": nbytes, "ms": t * 1e3, "achieved": nbytes / t / 1e9}
+    for r in res.values():
+        r["unit"] = "GB/s"
+        r["peak"] = hbm_peak
+        r["frac"] = r["achieved"] / hbm_peak
+        r["peak_kind"] = f"of {peak_kind} (copy)"
+    return res
+
+
 def cpu_baseline(w):
-    import numpy as np
+    import torch
 
     from oracle import usp_oracle as O
 
     cores = os.cpu_count() or 1
-    S, D = w["S"], w["D"]
-    rng = np.random.default_rng(0)
-    heads, total, fl = 4, 0.0, 0.0
+    torch.set_num_threads(cores)
+    S, D, heads = w["S"], w["D"], w["H"]
+    if S > 20000:
+        S, heads = 9450, 8  # a shard-sized sample: the full score matrix is too much for a bounded host run
+    g = torch.Generator().manual_seed(0)
+    total, fl, reps = 0.0, 0.0, 0
+    q, k, v = (torch.randn(1, heads, S, D, generator=g) for _ in range(3))
+    O.attention_dense_torch_cpu(q, k, v)  # warm-up
     t_end = time.perf_counter() + 12.0
-    reps = 0
-    while time.perf_counter() < t_end and reps < 6:
-        q, k, v = (rng.standard_normal((1, heads, S, D), dtype=np.float32) for _ in range(3))
+    while time.perf_counter() < t_end and reps < 20:
         t0 = time.perf_counter()
-        O.attention_dense(q, k, v, dtype=np.float32)
+        O.attention_dense_torch_cpu(q, k, v)
         total += time.perf_counter() - t0
         fl += 4.0 * S * S * heads * D
         reps += 1
     return {"value": fl / total / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
-            "sample": f"{reps} x ({heads} of {w['H']} heads, {S} tokens) of one layer, fp32 numpy/BLAS oracle"}
+            "sample": f"{reps} x one layer call ({heads} heads, {S} tokens, fp32), torch CPU SDPA as the "
+                      f"reference's SDPA back-end calls it, {cores} threads"}
 
 
 def main():
@@ -283,6 +339,7 @@ def main():
     ap.add_argument("--workload", default="flux", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary workload and the CPU baseline")
+    ap.add_argument("--layers", type=int, default=0, help="time only this many layers per step (profiling aid)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     name = args.workload
@@ -318,6 +375,8 @@ def main():
     assert ops.query_caps()["supported"] == 1, "not an sm_100 device"
 
     tf_peak, hbm_peak, peak_kind = peaks()
+    if args.layers > 0:
+        w = dict(w, layers=min(args.layers, w["layers"]))
     main_res = run_workload(torch, dist, xdit_b200, ops, name, w, args, device, rank, world, w["layers"], True)
     extra = {}
     if not args.no_extra:
@@ -335,6 +394,11 @@ def main():
             }
         except Exception as e:  # the secondary workload must not take the main line down
             extra[other] = {"error": repr(e)[:200]}
+        if world == 1:
+            try:
+                extra["hbm_kernels"] = hbm_kernels(torch, ops, device, hbm_peak, peak_kind)
+            except Exception as e:
+                extra["hbm_kernels"] = {"error": repr(e)[:200]}
 
     if rank == 0:
         calls = w["layers"]

@@ -22,6 +22,7 @@ import numpy as np
 
 __all__ = [
     "attention_dense",
+    "attention_dense_torch_cpu",
     "merge_out_lse",
     "all_to_all_single",
     "input_all_to_all",
@@ -48,9 +49,8 @@ def attention_dense(q, k, v, scale=None, causal=False, dtype=np.float64):
     k = np.asarray(k, dtype=dtype)
     v = np.asarray(v, dtype=dtype)
     d = q.shape[-1]
-    if scale is None:
-        scale = 1.0 / np.sqrt(d)
-    s = np.einsum("bhqd,bhkd->bhqk", q, k) * scale
+    scale = float(1.0 / np.sqrt(d)) if scale is None else float(scale)  # python float: keeps `dtype`
+    s = np.matmul(q, np.ascontiguousarray(np.swapaxes(k, -1, -2))) * scale
     if causal:
         sq, sk = s.shape[-2:]
         mask = np.arange(sk)[None, :] > np.arange(sq)[:, None]
@@ -59,10 +59,22 @@ def attention_dense(q, k, v, scale=None, causal=False, dtype=np.float64):
     m = np.where(np.isfinite(m), m, 0.0)
     p = np.exp(s - m)
     l = p.sum(axis=-1, keepdims=True)
-    out = np.einsum("bhqk,bhkd->bhqd", p, v) / np.where(l == 0, 1.0, l)
+    out = np.matmul(p, v) / np.where(l == 0, 1.0, l)
     with np.errstate(divide="ignore"):
         lse = (m + np.log(l))[..., 0]
     return out, lse
+
+
+def attention_dense_torch_cpu(q, k, v, causal=False):
+    """The reference's own CPU path for the dense call, restated: its ``SDPA`` back-end is a bare
+    ``F.scaled_dot_product_attention(query, key, value, dropout_p=0, is_causal=...)``
+    (``xfuser/core/distributed/attention_backend.py:492-502``), which on CPU tensors runs torch's
+    fused CPU kernel on all host threads.  Used for the timed CPU baseline; parity checks use
+    the float64 numpy functions of this module."""
+    import torch
+    import torch.nn.functional as F
+
+    return F.scaled_dot_product_attention(q, k, v, dropout_p=0.0, is_causal=causal)
 
 
 def _sigmoid(x):

@@ -1,0 +1,124 @@
+"""Per-rank body shared by the gloo (CPU, stand-in kernels) and NCCL (GPU, real kernels) USP tests:
+replays the golden fixtures produced by the unmodified reference through xdit_b200."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+
+
+def worker(rank, world, port, files, mode, errq, backend="gloo", dtype_name="float32", tol=5e-5):
+    try:
+        sys.path.insert(0, ROOT)
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        gpu = backend == "nccl"
+        if gpu:
+            torch.cuda.set_device(rank)
+            dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        else:
+            dist.init_process_group("gloo", rank=rank, world_size=world)
+            torch.set_num_threads(1)
+        import xdit_b200
+
+        if gpu:
+            from xdit_b200 import ops
+        else:
+            from tests import fake_ops
+
+            fake_ops.install()
+        dtype = getattr(torch, dtype_name)
+        dev = torch.device("cuda", rank) if gpu else torch.device("cpu")
+        put = lambda a: torch.from_numpy(a).to(dtype).to(dev)
+        for path in files:
+            z = np.load(path)
+            U, R, B, H, D, S, Sj, Sk = [int(x) for x in z["meta"]]
+            strat = str(z["strategy"])
+            strat = None if strat == "none" else strat
+            P = U * R
+            xdit_b200.init_sequence_parallel(U, R, backend=backend)
+            q, k, v = (put(z[n]) for n in ("q", "k", "v"))
+            ql, kl, vl = (t.chunk(P, dim=2)[rank] for t in (q, k, v))
+            kw = {}
+            if strat:
+                kw = dict(joint_query=put(z["jq"]), joint_key=put(z["jk"]), joint_value=put(z["jv"]),
+                          joint_strategy=strat)
+            if mode == "usp":
+                # transposed views, as the DiT processors pass them (transformer_flux.py:170-172)
+                ql, kl, vl = (t.transpose(1, 2).contiguous().transpose(1, 2) for t in (ql, kl, vl))
+                out = xdit_b200.USP(ql, kl, vl, **kw)
+            elif mode == "compat":
+                from xdit_b200.attention_backend import AttentionBackendType, register_attention_function
+
+                if gpu:
+                    from xdit_b200 import ops as _ops
+
+                    def _custom(query, key, value, dropout_p, is_causal, attention_kwargs=None):
+                        return _ops.attn_fwd(query, key, value, want_lse=True, force_generic=True)
+                else:
+                    def _custom(query, key, value, dropout_p, is_causal, attention_kwargs=None):
+                        return fake_ops.attn_fwd(query, key, value, want_lse=True)
+
+                register_attention_function(AttentionBackendType.SAGE)(_custom)
+                out = xdit_b200.USP(ql, kl, vl, backend=AttentionBackendType.SAGE, combine_qkv_a2a=True, **kw)
+            else:  # legacy [B,S,H,D] layer
+                layer = xdit_b200.xFuserLongContextAttention()
+                t = lambda x: x.transpose(1, 2)
+                kw2 = {}
+                if strat:
+                    kw2 = dict(joint_tensor_query=t(kw["joint_query"]), joint_tensor_key=t(kw["joint_key"]),
+                               joint_tensor_value=t(kw["joint_value"]), joint_strategy=strat)
+                out = t(layer(None, t(ql), t(kl), t(vl), **kw2))
+            if gpu:
+                torch.cuda.synchronize()
+                ops.check_status()
+            ref = torch.from_numpy(z["out"][rank]).double()
+            assert tuple(out.shape) == tuple(ref.shape), (path, out.shape, ref.shape)
+            got = out.detach().double().cpu()
+            assert torch.isfinite(got).all(), (os.path.basename(path), mode, rank, "non-finite")
+            err = (got - ref).abs().max().item()
+            assert err < tol, (os.path.basename(path), mode, rank, err)
+            dist.barrier()
+        dist.destroy_process_group()
+    except Exception as e:  # surface the failure in the parent
+        import traceback
+
+        errq.put(f"rank {rank}: {e}\n{traceback.format_exc()}")
+        raise
+
+
+def run(world, files, mode, port, **kw):
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    errq = ctx.SimpleQueue()
+    procs = [ctx.Process(target=worker, args=(r, world, port, files, mode, errq), kwargs=kw) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(600)
+    msgs = []
+    while not errq.empty():
+        msgs.append(errq.get())
+    alive = [p for p in procs if p.is_alive()]
+    for p in alive:
+        p.terminate()
+    assert not msgs, "\n".join(msgs)
+    assert not alive, "ranks did not finish"
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+
+
+def golden_files(world):
+    import glob
+
+    out = []
+    for f in sorted(glob.glob(os.path.join(HERE, "golden", "usp_*.npz"))):
+        m = np.load(f)["meta"]
+        if int(m[0]) * int(m[1]) == world:
+            out.append(f)
+    return out
