@@ -32,6 +32,7 @@
 #include <cmath>
 #include <cstring>
 #include <mutex>
+#include <type_traits>
 
 #include "common.cuh"
 
@@ -43,12 +44,16 @@ constexpr int kTile = 128;
 constexpr int kThreads = 320;
 constexpr int kSlabBytes = kTile * 128;       // one 64-element slab of a 128-row tile
 constexpr int kBoxBytes = kChunk * 128;       // one TMA box: 64 rows x 64 elements
-constexpr uint64_t kWaitLimitNs = 4000000000ull;
+constexpr uint64_t kWaitLimitNs = 200000000ull;  // 0.2 s: no legitimate wait comes near this
+#ifndef XDIT_EMU_PAIRS
+#define XDIT_EMU_PAIRS 0
+#endif
+constexpr int kEmuPairs = XDIT_EMU_PAIRS;  // of every 4 column pairs, how many take the polynomial exp2
 
 struct alignas(64) Sm100Args {
   CUtensorMap tm_q, tm_k, tm_v, tm_k2, tm_v2;
   int32_t q_seg_len, q_cps, q_chunks;
-  int32_t k_seg_len, k_cps, k_chunks_main, k2_len, kv_chunks, n_kv_tiles;
+  int32_t k_seg_len, k_cps, k_chunks_main, k2_len, kv_chunks, n_kv_tiles, k_tail, k2_tail;
   int32_t H, D, dk16, dv_n;
   int32_t sq_total;
   float scale_log2;
@@ -61,6 +66,7 @@ struct alignas(64) Sm100Args {
   int32_t* status;
 #ifdef XDIT_DEBUG_DUMP
   float* dbg_s;  // [2][128][128] raw S of key tile 0 of CTA (0,0,0), then [2][128][128] raw O
+  long long* dbg_t;  // timeline of CTA (0,0,0): [3 roles][64 iterations][8 events] clock64 stamps
 #endif
 };
 
@@ -106,6 +112,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       return false;
     }
   }
+}
+// A launch whose status word is already set (an earlier CTA or launch timed out) does no work:
+// it keeps a failure from costing one time limit per CTA.
+__device__ __forceinline__ bool status_is_set(const int32_t* status) {
+  return status != nullptr && *reinterpret_cast<const volatile int32_t*>(status) != 0;
 }
 __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int c0,
                                             int c1, int c2, int c3, int c4) {
@@ -159,9 +170,85 @@ __device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ float ex2(float x) {
+#ifdef XDIT_EXP_NOEX2
+  return x * 0.001f + 1.0f;
+#endif
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+#ifdef XDIT_DEBUG_DUMP
+#define XDIT_TRACE(role, it, ev)                                                                   \
+  do {                                                                                             \
+    if (a.dbg_t && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (it) < 64 && lane == 0 && \
+        ((role) == 2 || (warp & 3) == 0))                                                          \
+      a.dbg_t[((role) * 64 + (it)) * 8 + (ev)] = clock64();                                        \
+  } while (0)
+#define XDIT_TRACE_DEP(role, it, ev, dep)                                                          \
+  do {                                                                                             \
+    long long t_;                                                                                  \
+    asm volatile("mov.u64 %0, %%clock64;" : "=l"(t_) : "r"(dep) : "memory");                       \
+    if (a.dbg_t && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (it) < 64 && lane == 0 && \
+        ((role) == 2 || (warp & 3) == 0))                                                          \
+      a.dbg_t[((role) * 64 + (it)) * 8 + (ev)] = t_;                                               \
+  } while (0)
+#else
+#define XDIT_TRACE(role, it, ev) do {} while (0)
+#define XDIT_TRACE_DEP(role, it, ev, dep) do {} while (0)
+#endif
+__device__ __forceinline__ float max3(float a, float b, float c) {
+#ifdef XDIT_EXP_MAX2
+  return fmaxf(a, fmaxf(b, c));
+#else
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+#endif
+}
+// packed fp32 pairs (one 64-bit register): halves the issue slots of the softmax arithmetic
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t x, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(x));
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+// 2^x for a pair on the FMA/ALU pipes instead of the special-function unit: x = n + f with
+// n = round(x) taken from the mantissa of x + 1.5*2^23, 2^f by a cubic (relative error 7.5e-5,
+// far below the 16-bit P it feeds), n added into the exponent field.  x is clamped at -126 so
+// that the exponent field cannot wrap.
+__device__ __forceinline__ uint64_t ex2_emu2(uint64_t x2) {
+  float x0, x1;
+  f2_unpack(x2, x0, x1);
+  x0 = fmaxf(x0, -126.f);
+  x1 = fmaxf(x1, -126.f);
+  const uint64_t xc = f2_pack(x0, x1);
+  const uint64_t magic = f2_pack(12582912.f, 12582912.f);
+  const uint64_t t2 = f2_add(xc, magic);
+  const uint64_t n2 = f2_add(t2, f2_pack(-12582912.f, -12582912.f));
+  const uint64_t f2 = f2_fma(n2, f2_pack(-1.f, -1.f), xc);
+  uint64_t p2 = f2_fma(f2, f2_pack(0.05517132207751274f, 0.05517132207751274f),
+                       f2_pack(0.24261054396629333f, 0.24261054396629333f));
+  p2 = f2_fma(p2, f2, f2_pack(0.6932609677314758f, 0.6932609677314758f));
+  p2 = f2_fma(p2, f2, f2_pack(0.9999281167984009f, 0.9999281167984009f));
+  float p0, p1, t0, t1;
+  f2_unpack(p2, p0, p1);
+  f2_unpack(t2, t0, t1);
+  p0 = __uint_as_float(__float_as_uint(p0) + (__float_as_uint(t0) << 23));
+  p1 = __uint_as_float(__float_as_uint(p1) + (__float_as_uint(t1) << 23));
+  return f2_pack(p0, p1);
 }
 
 // Shared-memory matrix descriptors (sm_100 format: version 1 at bit 46, 128-byte swizzle = 2 at
@@ -186,6 +273,12 @@ __device__ __forceinline__ uint32_t make_idesc(bool bf16, bool b_mn_major, int n
 
 template <bool BF16>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+#ifdef XDIT_EXP_PRMT_PACK
+  if constexpr (BF16) {
+    // round-half-up to bf16 on the integer pipe: add half an ulp, keep the upper 16 bits
+    return __byte_perm(__float_as_uint(lo) + 0x8000u, __float_as_uint(hi) + 0x8000u, 0x7632);
+  }
+#endif
   if constexpr (BF16) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -226,8 +319,8 @@ struct SmemLayout {
   static constexpr int kQOff = 0;
   static constexpr int kKvOff = 2 * kQTileBytes;
   static constexpr int kBarOff = kKvOff + NSTAGE * kStageBytes;
-  // barriers: q_full[2], kv_full[NSTAGE], kv_empty[NSTAGE], s_full[2], p_full[2], o_full[2], drain
-  static constexpr int kNumBars = 2 + 2 * NSTAGE + 2 + 2 + 2 + 1;
+  // barriers: q_full[2], kv_full[NSTAGE], kv_empty[NSTAGE], s_full[2], p_full[2][2], o_full[2], drain
+  static constexpr int kNumBars = 2 + 2 * NSTAGE + 2 + 4 + 2 + 1;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
   static constexpr int kTotal = kMiscOff + 16;
   static constexpr int kDynamic = kTotal + 1024;  // slack to align the base to 1024 bytes
@@ -251,9 +344,11 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_sm100_kernel(const __gri
   auto bar_kv_full = [&](int s) { return bar0 + 8u * (2 + s); };
   auto bar_kv_empty = [&](int s) { return bar0 + 8u * (2 + NSTAGE + s); };
   auto bar_s_full = [&](int t) { return bar0 + 8u * (2 + 2 * NSTAGE + t); };
-  auto bar_p_full = [&](int t) { return bar0 + 8u * (4 + 2 * NSTAGE + t); };
-  auto bar_o_full = [&](int t) { return bar0 + 8u * (6 + 2 * NSTAGE + t); };
-  const uint32_t bar_drain = bar0 + 8u * (8 + 2 * NSTAGE);
+  // P of a key tile is published in two halves of 64 key columns, one barrier each (a waiter on
+  // an mbarrier may fall at most one phase behind, so the halves cannot share one barrier)
+  auto bar_p_full = [&](int t, int half) { return bar0 + 8u * (4 + 2 * NSTAGE + 2 * t + half); };
+  auto bar_o_full = [&](int t) { return bar0 + 8u * (8 + 2 * NSTAGE + t); };
+  const uint32_t bar_drain = bar0 + 8u * (10 + 2 * NSTAGE);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + L::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + L::kMiscOff + 4);
 
@@ -267,7 +362,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_sm100_kernel(const __gri
     for (int t = 0; t < 2; ++t) {
       mbar_init(bar_q_full(t), 1);
       mbar_init(bar_s_full(t), 1);
-      mbar_init(bar_p_full(t), 128);
+      mbar_init(bar_p_full(t, 0), 128);
+      mbar_init(bar_p_full(t, 1), 128);
       mbar_init(bar_o_full(t), 1);
     }
     for (int s = 0; s < NSTAGE; ++s) {
@@ -275,7 +371,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_sm100_kernel(const __gri
       mbar_init(bar_kv_empty(s), 1);
     }
     mbar_init(bar_drain, 1);
-    *abort_flag = 0;
+    *abort_flag = status_is_set(a.status) ? -1 : 0;  // -1: skip all work (an earlier failure is pending)
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 8) {
@@ -286,8 +382,11 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_sm100_kernel(const __gri
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  const bool skip = *abort_flag != 0;  // same value for every thread: written before the barrier above
 
-  if (warp == 9) {
+  if (skip) {
+    // nothing to do: fall through to the teardown, which frees TMEM
+  } else if (warp == 9) {
     // ======================= TMA producer =======================
     if (lane == 0) {
       int issued = 0;  // ring items armed so far
@@ -352,9 +451,10 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_sm100_kernel(const __gri
           tc_mma_ss(tmem_base + t * kTile, desc_kmajor(qa + off), desc_kmajor(kb + off), idesc_qk, ks > 0);
         }
       };
-      auto issue_pv = [&](int t, int stage, bool first_tile) {
+      // O_t += P_t[:, 64*half : 64*half+64] V[64*half : 64*half+64, :]   (4 steps of 16 key rows)
+      auto issue_pv_half = [&](int t, int stage, int half, bool first_tile) {
         const uint32_t vb = kv_smem + stage * L::kStageBytes;
-        for (int ks = 0; ks < kTile / 16; ++ks)
+        for (int ks = 4 * half; ks < 4 * half + 4; ++ks)
           tc_mma_ts(tmem_base + 256 + t * kTile, tmem_base + t * kTile + ks * 8, desc_mnmajor(vb + ks * 2048),
                     idesc_pv, (!first_tile) || ks > 0);
       };
@@ -376,11 +476,20 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_sm100_kernel(const __gri
         ok = mbar_wait(bar_kv_full(sv), (iv / NSTAGE) & 1, abort_flag, 210);
         for (int t = 0; t < 2 && ok; ++t) {
           if (!tile_on[t]) continue;
-          ok = mbar_wait(bar_p_full(t), j & 1, abort_flag, 220 + t);
+          // P arrives in two halves (64 key columns each): the first half of O += P V runs while
+          // the softmax group still computes the second half
+          ok = mbar_wait(bar_p_full(t, 0), j & 1, abort_flag, 220 + t);
           if (!ok) break;
           tc_fence_after();
-          issue_pv(t, sv, j == 0);
-          tc_commit(bar_o_full(t));
+          if (t == 0) XDIT_TRACE(2, j, 0);
+          issue_pv_half(t, sv, 0, j == 0);
+          if (t == 0) XDIT_TRACE(2, j, 1);
+          ok = mbar_wait(bar_p_full(t, 1), j & 1, abort_flag, 222 + t);
+          if (!ok) break;
+          tc_fence_after();
+          if (t == 0) XDIT_TRACE(2, j, 2);
+          issue_pv_half(t, sv, 1, j == 0);
+          if (t == 0) XDIT_TRACE(2, j, 3);
           if (t == last_t) tc_commit(bar_kv_empty(sv));  // V(j) is free once both tiles' PV retire
           if (more) {
             if (t == 0 || !tile_on[0]) {
@@ -388,8 +497,15 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_sm100_kernel(const __gri
               if (!ok) break;
               tc_fence_after();
             }
+            if (t == 0) XDIT_TRACE(2, j, 4);
             issue_qk(t, sk);
+            if (t == 0) XDIT_TRACE(2, j, 5);
+            // completes after every MMA issued so far, i.e. it also tells the softmax group that
+            // O_t holds the sum up to key tile j
             tc_commit(bar_s_full(t));
+            if (t == 0) XDIT_TRACE(2, j, 6);
+          } else {
+            tc_commit(bar_o_full(t));
           }
         }
         if (!ok) break;
@@ -413,86 +529,141 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_sm100_kernel(const __gri
     float m_run = -INFINITY;  // running reference maximum, in scaled log2 units
     float l_run = 0.f;
     const float sl2 = a.scale_log2;
+    // valid key columns of the next chunk, tracked without divisions
+    int cidx = 0, cpos = 0;
+    auto next_valid = [&]() -> int {
+      int v;
+      if (cidx < a.k_chunks_main) {
+        v = (cpos == a.k_cps - 1) ? a.k_tail : kChunk;
+        if (++cpos == a.k_cps) cpos = 0;
+      } else if (cidx < a.kv_chunks) {
+        v = (cidx == a.kv_chunks - 1) ? a.k2_tail : kChunk;
+      } else {
+        v = 0;
+      }
+      ++cidx;
+      return v;
+    };
+    // One key tile for this thread's query row.  MASKED is a compile-time switch so that full
+    // tiles carry no masking instructions at all.
+    auto softmax_tile = [&](auto masked_tag, int j, int v0, int v1) -> bool {
+      constexpr bool MASKED = decltype(masked_tag)::value;
+      tc_fence_after();
+      XDIT_TRACE(t, j, 0);
+      uint32_t s[128];
+      XDIT_TMEM_LD32(s, 0, tmem_s + 0);
+      XDIT_TMEM_LD32(s, 32, tmem_s + 32);
+      XDIT_TMEM_LD32(s, 64, tmem_s + 64);
+      XDIT_TMEM_LD32(s, 96, tmem_s + 96);
+      tmem_wait_ld();
+      XDIT_TRACE_DEP(t, j, 1, s[0] ^ s[33] ^ s[66] ^ s[127]);
+#ifdef XDIT_DEBUG_DUMP
+      if (a.dbg_s && j == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+        for (int c = 0; c < 128; ++c) a.dbg_s[(t * 128 + row) * 128 + c] = __uint_as_float(s[c]);
+      }
+#endif
+      if constexpr (MASKED) {
+#pragma unroll
+        for (int c = 0; c < 128; ++c) {
+          const bool dead = (c < 64) ? (c >= v0) : (c - 64 >= v1);
+          if (dead) s[c] = 0xff800000u;  // -inf
+        }
+      }
+      float mx0 = max3(__uint_as_float(s[0]), __uint_as_float(s[1]), __uint_as_float(s[2]));
+      float mx1 = max3(__uint_as_float(s[3]), __uint_as_float(s[4]), __uint_as_float(s[5]));
+      float mx2 = max3(__uint_as_float(s[6]), __uint_as_float(s[7]), __uint_as_float(s[8]));
+      float mx3 = max3(__uint_as_float(s[9]), __uint_as_float(s[10]), __uint_as_float(s[11]));
+#pragma unroll
+      for (int c = 12; c < 124; c += 8) {
+        mx0 = max3(mx0, __uint_as_float(s[c]), __uint_as_float(s[c + 1]));
+        mx1 = max3(mx1, __uint_as_float(s[c + 2]), __uint_as_float(s[c + 3]));
+        mx2 = max3(mx2, __uint_as_float(s[c + 4]), __uint_as_float(s[c + 5]));
+        mx3 = max3(mx3, __uint_as_float(s[c + 6]), __uint_as_float(s[c + 7]));
+      }
+      mx0 = max3(mx0, __uint_as_float(s[124]), __uint_as_float(s[125]));
+      mx1 = max3(mx1, __uint_as_float(s[126]), __uint_as_float(s[127]));
+      const float mt = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sl2;
+      XDIT_TRACE_DEP(t, j, 2, __float_as_uint(mt));
+      if (j == 0) {
+        m_run = mt;
+      } else {
+        // Lazy rescale: keep the old reference maximum unless some row of this warp grew by
+        // more than 2^8; exp2 of at most 8 is safe in fp32 and in the 16-bit P.  S_t(j) being
+        // complete implies that O_t += P V of tile j-1 has retired, so O may be touched here.
+        const bool grow = mt > m_run + 8.f;
+        if (__any_sync(0xffffffffu, grow)) {
+          const float m_new = fmaxf(m_run, mt);
+          const float alpha = ex2(m_run - m_new);
+          for (int c0 = 0; c0 < a.dv_n; c0 += 32) {
+            uint32_t o[32];
+            XDIT_TMEM_LD32(o, 0, tmem_o + c0);
+            tmem_wait_ld();
+#pragma unroll
+            for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
+            XDIT_TMEM_ST32(o, 0, tmem_o + c0);
+          }
+          tmem_wait_st();
+          l_run *= alpha;
+          m_run = m_new;
+        }
+      }
+      // P = 2^(s*scale - m): in every group of 8 columns kEmuPairs pairs go through the
+      // polynomial on the FMA pipe and the rest through ex2 on the special-function unit.
+      // P is handed to the tensor core in two halves of 64 key columns.
+      const uint64_t sl2_2 = f2_pack(sl2, sl2), negm_2 = f2_pack(-m_run, -m_run);
+      uint64_t sum_a = f2_pack(0.f, 0.f), sum_b = sum_a;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t pk[32];
+#pragma unroll
+        for (int c = 64 * half; c < 64 * half + 64; c += 8) {
+#pragma unroll
+          for (int pr = 0; pr < 4; ++pr) {
+            const int e = c + 2 * pr;
+            uint64_t x2 = f2_fma(f2_pack(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), sl2_2, negm_2);
+            uint64_t p2;
+            if (pr < kEmuPairs) {
+              p2 = ex2_emu2(x2);
+            } else {
+              float x0, x1;
+              f2_unpack(x2, x0, x1);
+              p2 = f2_pack(ex2(x0), ex2(x1));
+            }
+            if (pr & 1) sum_b = f2_add(sum_b, p2); else sum_a = f2_add(sum_a, p2);
+            float p0, p1;
+            f2_unpack(p2, p0, p1);
+            pk[(e - 64 * half) / 2] = pack2<BF16>(p0, p1);
+          }
+        }
+        if (half == 0) XDIT_TRACE_DEP(t, j, 3, pk[0] ^ pk[31]);
+        XDIT_TMEM_ST32(pk, 0, tmem_s + 32 * half);
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(bar_p_full(t, half));
+        if (half == 0) XDIT_TRACE(t, j, 4);
+      }
+      {
+        float a0, a1;
+        f2_unpack(f2_add(sum_a, sum_b), a0, a1);
+        l_run += a0 + a1;
+      }
+      XDIT_TRACE(t, j, 5);
+      return true;
+    };
     if (tile_on[t]) {
       for (int j = 0; j < n_tiles; ++j) {
         ok = __all_sync(0xffffffffu, mbar_wait(bar_s_full(t), j & 1, abort_flag, 300 + t));
         if (!ok) break;
-        tc_fence_after();
-        uint32_t s[128];
-        XDIT_TMEM_LD32(s, 0, tmem_s + 0);
-        XDIT_TMEM_LD32(s, 32, tmem_s + 32);
-        XDIT_TMEM_LD32(s, 64, tmem_s + 64);
-        XDIT_TMEM_LD32(s, 96, tmem_s + 96);
-        tmem_wait_ld();
-#ifdef XDIT_DEBUG_DUMP
-        if (a.dbg_s && j == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
-          for (int c = 0; c < 128; ++c) a.dbg_s[(t * 128 + row) * 128 + c] = __uint_as_float(s[c]);
-        }
+#ifdef XDIT_EXP_NOMASK
+        const int v0 = kChunk, v1 = kChunk;
+#else
+        const int v0 = next_valid(), v1 = next_valid();
 #endif
-        const int v0 = kv_chunk(a, 2 * j).valid, v1 = kv_chunk(a, 2 * j + 1).valid;
-        if (v0 < kChunk || v1 < kChunk) {
-#pragma unroll
-          for (int c = 0; c < 128; ++c) {
-            const bool dead = (c < 64) ? (c >= v0) : (c - 64 >= v1);
-            if (dead) s[c] = 0xff800000u;  // -inf
-          }
-        }
-        float mx0 = __uint_as_float(s[0]), mx1 = __uint_as_float(s[1]), mx2 = __uint_as_float(s[2]),
-              mx3 = __uint_as_float(s[3]);
-#pragma unroll
-        for (int c = 4; c < 128; c += 4) {
-          mx0 = fmaxf(mx0, __uint_as_float(s[c]));
-          mx1 = fmaxf(mx1, __uint_as_float(s[c + 1]));
-          mx2 = fmaxf(mx2, __uint_as_float(s[c + 2]));
-          mx3 = fmaxf(mx3, __uint_as_float(s[c + 3]));
-        }
-        const float mt = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sl2;
-        if (j == 0) {
-          m_run = mt;
-        } else {
-          // Lazy rescale: keep the old reference maximum unless some row of this warp grew by
-          // more than 2^8; exp2 of at most 8 is safe in fp32 and in the 16-bit P.
-          const bool grow = mt > m_run + 8.f;
-          if (__any_sync(0xffffffffu, grow)) {
-            const float m_new = fmaxf(m_run, mt);
-            const float alpha = ex2(m_run - m_new);
-            ok = __all_sync(0xffffffffu, mbar_wait(bar_o_full(t), (j - 1) & 1, abort_flag, 310 + t));
-            if (!ok) break;
-            tc_fence_after();
-            for (int c0 = 0; c0 < a.dv_n; c0 += 32) {
-              uint32_t o[32];
-              XDIT_TMEM_LD32(o, 0, tmem_o + c0);
-              tmem_wait_ld();
-#pragma unroll
-              for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
-              XDIT_TMEM_ST32(o, 0, tmem_o + c0);
-            }
-            tmem_wait_st();
-            l_run *= alpha;
-            m_run = m_new;
-          }
-        }
-        float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
-        uint32_t pk[64];
-#pragma unroll
-        for (int c = 0; c < 128; c += 4) {
-          const float p0 = ex2(fmaf(__uint_as_float(s[c]), sl2, -m_run));
-          const float p1 = ex2(fmaf(__uint_as_float(s[c + 1]), sl2, -m_run));
-          const float p2 = ex2(fmaf(__uint_as_float(s[c + 2]), sl2, -m_run));
-          const float p3 = ex2(fmaf(__uint_as_float(s[c + 3]), sl2, -m_run));
-          sum0 += p0; sum1 += p1; sum2 += p2; sum3 += p3;
-          pk[c / 2] = pack2<BF16>(p0, p1);
-          pk[c / 2 + 1] = pack2<BF16>(p2, p3);
-        }
-        l_run += (sum0 + sum1) + (sum2 + sum3);
-        XDIT_TMEM_ST32(pk, 0, tmem_s + 0);
-        XDIT_TMEM_ST32(pk, 32, tmem_s + 32);
-        tmem_wait_st();
-        tc_fence_before();
-        mbar_arrive(bar_p_full(t));
+        if (v0 < kChunk || v1 < kChunk) softmax_tile(std::true_type{}, j, v0, v1);
+        else softmax_tile(std::false_type{}, j, v0, v1);
       }
       // ---------------- epilogue ----------------
-      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_o_full(t), (n_tiles - 1) & 1, abort_flag, 320 + t));
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_o_full(t), 0, abort_flag, 320 + t));
       if (ok) {
         tc_fence_after();
         const int qc = 4 * pair + 2 * t + (row >> 6);
@@ -577,7 +748,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_sm100_kernel(const __gri
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
   }
-  if (threadIdx.x == 0 && *abort_flag && a.status) atomicCAS(a.status, 0, *abort_flag);
+  if (threadIdx.x == 0 && *abort_flag > 0 && a.status) atomicCAS(a.status, 0, *abort_flag);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -695,6 +866,8 @@ int launch_attn_sm100(const xdit_attn_params& p, cudaStream_t stream) {
   a.k2_len = p.k2.ptr ? p.k2.seg_len : 0;
   a.kv_chunks = a.k_chunks_main + (a.k2_len + kChunk - 1) / kChunk;
   a.n_kv_tiles = (a.kv_chunks + 1) / 2;
+  a.k_tail = a.k_seg_len - (a.k_cps - 1) * kChunk;
+  a.k2_tail = a.k2_len ? a.k2_len - ((a.k2_len + kChunk - 1) / kChunk - 1) * kChunk : 0;
   a.H = p.H;
   a.D = p.D;
   a.dk16 = (p.D + 15) / 16;
@@ -711,6 +884,7 @@ int launch_attn_sm100(const xdit_attn_params& p, cudaStream_t stream) {
 #ifdef XDIT_DEBUG_DUMP
   extern float* g_xdit_dbg_s;
   a.dbg_s = g_xdit_dbg_s;
+  a.dbg_t = g_xdit_dbg_s ? reinterpret_cast<long long*>(g_xdit_dbg_s + 4 * 128 * 128 + 256) : nullptr;
 #endif
   dim3 grid((a.q_chunks + 3) / 4, p.H, p.B);
   const bool bf16 = p.dtype == XDIT_BF16;
