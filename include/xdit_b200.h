@@ -108,6 +108,31 @@ XDIT_API int xdit_attn_fwd(const struct xdit_attn_params* p, void* stream);
  * 0 = CUDA-core kernel, negative = the error the call would return. */
 XDIT_API int xdit_attn_which(const struct xdit_attn_params* p);
 
+/* Ring-step attention for callers that cannot allocate device memory.
+ *
+ * No counterpart in the reference (which allocates its merge buffers through torch).  Some
+ * hosts of this library have no allocator to offer at the point of the call: a C or C++ serving
+ * loop that was handed fixed input/output buffers, a plugin running under a framework whose
+ * allocator it must not touch, or code that runs while allocation is forbidden.  For them this
+ * variant of xdit_attn_fwd keeps the fp32 running accumulators of a ring sequence (what
+ * xdit_attn_fwd takes as o_acc / lse_acc) in an array that is part of the library image
+ * (XDIT_STATIC_ACC_FLOATS floats = 32 MiB, held by every GPU that loads the library until the
+ * process exits).  The caller still passes q, k, v, the joint k2/v2, out and lse.
+ *
+ *   - p->o_acc and p->lse_acc must be NULL; at least one of acc_in / acc_out must be set
+ *     (first step: acc_in=0, acc_out=1; middle steps: 1,1; last step: acc_in=1, acc_out=0);
+ *   - B*H*Sq*D (rounded up to 64) + B*H*Sq floats must fit in XDIT_STATIC_ACC_FLOATS, otherwise
+ *     the call returns XDIT_E_SHAPE and launches nothing;
+ *   - the function calls no cudaMalloc/cudaFree and no allocating library routine.  The first
+ *     call on each device looks the array's device address up (cudaGetSymbolAddress with that
+ *     device current) and caches it; make that first call before starting a stream capture;
+ *   - every call on a device shares the one array and the array keeps what the last call left.
+ *     Nothing needs clearing as long as each sequence starts with acc_in=0, which overwrites the
+ *     rows it uses.  Two sequences whose kernels overlap on the GPU (different streams, or
+ *     interleaved steps) race on the array: keep one sequence at a time per device. */
+#define XDIT_STATIC_ACC_FLOATS (8 * 1024 * 1024)
+XDIT_API int xdit_attn_fwd_static_acc(const struct xdit_attn_params* p, void* stream);
+
 /* Ulysses input pack: [B,H,s,D] (any strides) plus optional joint rows -> the all-to-all send
  * buffer, peer-major.  For peer p the block at dst + p*dst_peer_stride holds
  * [H/U][B][s + s_joint][D] contiguous, i.e. heads [p*H/U,(p+1)*H/U) of the source; joint rows

@@ -14,12 +14,14 @@ LIB_PATH = os.path.join(_PKG, "libxdit_b200.so")
 
 XDIT_BF16, XDIT_F16, XDIT_F32 = 0, 1, 2
 XDIT_MAX_PACK_JOBS = 4
+XDIT_STATIC_ACC_FLOATS = 8 * 1024 * 1024
 
 EXPORTS = [
     "xdit_query_caps",
     "xdit_last_error_string",
     "xdit_attn_fwd",
     "xdit_attn_which",
+    "xdit_attn_fwd_static_acc",
     "xdit_ulysses_pack",
     "xdit_ulysses_pack_out",
     "xdit_ulysses_unpack_out",
@@ -100,6 +102,8 @@ def load() -> C.CDLL:
     lib.xdit_last_error_string.restype = C.c_char_p
     lib.xdit_attn_fwd.argtypes = [C.POINTER(AttnParams), C.c_void_p]
     lib.xdit_attn_fwd.restype = C.c_int
+    lib.xdit_attn_fwd_static_acc.argtypes = [C.POINTER(AttnParams), C.c_void_p]
+    lib.xdit_attn_fwd_static_acc.restype = C.c_int
     lib.xdit_attn_which.argtypes = [C.POINTER(AttnParams)]
     lib.xdit_attn_which.restype = C.c_int
     lib.xdit_ulysses_pack.argtypes = [C.POINTER(PackJob), C.c_int32, C.c_int32, C.c_int32, C.c_int32,

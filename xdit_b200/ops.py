@@ -139,6 +139,25 @@ def attn_fwd(q, k, v, k2=None, v2=None, *, out=None, lse=None, o_acc=None, lse_a
     return out, lse
 
 
+def attn_fwd_static_acc(q, k, v, k2=None, v2=None, *, out=None, lse=None, acc_in=False, acc_out=False,
+                        scale=None, force_generic=False):
+    """One ring step through ``xdit_attn_fwd_static_acc``: like :func:`attn_fwd` with ``o_acc`` /
+    ``lse_acc``, but the fp32 running accumulators live in a fixed array inside the library, so
+    this wrapper allocates nothing.  ``out`` (and ``lse`` if wanted) must be passed for the last
+    step (``acc_out=False``).  One sequence at a time per device; sizes beyond the built-in
+    array raise ``XditError``."""
+    global launch_count
+    _require_cuda(q, k, v, k2, v2, out, lse)
+    if not acc_out and out is None:
+        raise ValueError("the last step (acc_out=False) needs an output tensor: this entry point allocates nothing")
+    p = _attn_params(q, k, v, k2, v2, out, lse, None, None, acc_in, acc_out, False, scale, force_generic)
+    p.status = status_buffer(q.device).data_ptr()
+    with torch.cuda.device(q.device):
+        _capi.check(_capi.load().xdit_attn_fwd_static_acc(C.byref(p), _stream(q)), "xdit_attn_fwd_static_acc")
+    launch_count += 1
+    return out, lse
+
+
 def attn_which(q, k, v, k2=None, v2=None, *, out=None, causal=False, acc=False) -> int:
     """1 when the tcgen05 kernel would serve this call, 0 for the CUDA-core kernel."""
     dummy = q if out is None else out
