@@ -6,6 +6,8 @@
 //   warps 4-7  softmax group for query tile 1
 //   warp  8    issues every tcgen05.mma (one lane) and owns the TMEM allocation
 //   warp  9    issues every TMA load (one lane)
+//   warps 10-11 idle: they complete the warpgroup that hands its registers to the softmax warps
+//               (setmaxnreg: 40 registers for warps 8-11, 232 for warps 0-7)
 // The tensor core alternates between the two query tiles, so that one tile's softmax runs while
 // the other tile's S = Q K^T and O += P V are in flight.
 //
@@ -41,7 +43,7 @@ namespace {
 
 constexpr int kChunk = 64;
 constexpr int kTile = 128;
-constexpr int kThreads = 320;
+constexpr int kThreads = 384;  // 8 softmax warps, MMA warp, TMA warp, 2 idle warps (full register-trading warpgroup)
 constexpr int kSlabBytes = kTile * 128;       // one 64-element slab of a 128-row tile
 constexpr int kBoxBytes = kChunk * 128;       // one TMA box: 64 rows x 64 elements
 constexpr uint64_t kWaitLimitNs = 200000000ull;  // 0.2 s: no legitimate wait comes near this
@@ -386,7 +388,10 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_sm100_kernel(const __gri
 
   if (skip) {
     // nothing to do: fall through to the teardown, which frees TMEM
-  } else if (warp == 9) {
+  } else if (warp >= 8) {
+    // warps 8-11 hand registers to the softmax warps: per scheduler 2 x 232 + 40 <= 512
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    if (warp == 9) {
     // ======================= TMA producer =======================
     if (lane == 0) {
       int issued = 0;  // ring items armed so far
@@ -435,7 +440,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_sm100_kernel(const __gri
             for (int it = 0; it < (1 << 20) && !mbar_try_wait(bar_q_full(t), 0); ++it) __nanosleep(64);
       }
     }
-  } else if (warp == 8) {
+    } else if (warp == 8) {
     // ======================= MMA issuer =======================
     if (lane == 0) {
       const uint32_t idesc_qk = make_idesc(BF16, false, kTile);
@@ -517,7 +522,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_sm100_kernel(const __gri
         for (int it = 0; it < (1 << 20) && !mbar_try_wait(bar_drain, 0); ++it) __nanosleep(64);
       }
     }
+    }
   } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
     // ======================= softmax + epilogue =======================
     const int t = warp >> 2;         // query tile of this warp group
     const int wq = warp & 3;         // TMEM lane quarter this warp may touch
