@@ -325,6 +325,107 @@ def hbm_kernels(torch, ops, device, hbm_peak, peak_kind):
     return res
 
 
+# --------------------------------------------------------------------------------------------
+# DiT step latency on random-init stand-ins of the named architectures (plain torch bf16 for
+# everything but attention; no checkpoint or diffusers is available here)
+# --------------------------------------------------------------------------------------------
+def dit_step_latency(torch, dist, xdit_b200, kind, device, rank, world, reps=5):
+    """One transformer forward (= one denoising step) of a Flux.1-dev-shaped MMDiT or a
+    Wan2.1-14B-shaped video DiT: QKV/out projections, q/k RMS-norm, RoPE, MLPs and norms in torch
+    bf16 with N(0, 0.02) weights, attention through ``xdit_b200.USP`` (text cross-attention through
+    ``xdit_b200.attention``), the sequence sharded over the ranks.  Returns milliseconds (median)."""
+    import torch.nn.functional as F
+
+    bf = torch.bfloat16
+    w = WORKLOADS[kind]
+    U, R = w["degrees"][world]
+    xdit_b200.init_sequence_parallel(U, R)
+    P = U * R
+    H, D, S = w["H"], w["D"], w["S"]
+    hid = H * D
+    s = S // P
+    g = torch.Generator(device=device)
+    g.manual_seed(0)
+
+    def lin(i, o):
+        return torch.randn(o, i, device=device, dtype=torch.float32, generator=g).mul_(0.02).to(bf)
+
+    def rms(x):  # over head_dim
+        return x * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-6).to(x.dtype)
+
+    cos = torch.randn(1, s, 1, D // 2, device=device, generator=g).cos().to(bf)
+    sin = torch.randn(1, s, 1, D // 2, device=device, generator=g).sin().to(bf)
+
+    def rope(x):  # x [B, s, H, D]
+        x1, x2 = x[..., : D // 2], x[..., D // 2:]
+        return torch.cat([x1 * cos - x2 * sin, x1 * sin + x2 * cos], -1)
+
+    def attn(q, k, v):  # [B, s, H, D] -> [B, s, H*D]
+        o = xdit_b200.USP(rope(rms(q)).transpose(1, 2), rope(rms(k)).transpose(1, 2), v.transpose(1, 2))
+        return o.transpose(1, 2).reshape(1, s, hid)
+
+    x = torch.randn(1, s, hid, device=device, generator=g).to(bf)
+    if kind == "flux":
+        mlp = 4 * hid
+        dbl = [dict(qkv=lin(hid, 3 * hid), proj=lin(hid, hid), up=lin(hid, mlp), down=lin(mlp, hid)) for _ in range(19)]
+        sgl = [dict(l1=lin(hid, 3 * hid + mlp), l2=lin(hid + mlp, hid)) for _ in range(38)]
+
+        def forward(x):
+            # text and image tokens form one sharded sequence; a double block differs from a single
+            # one by its separate attention/MLP projections (per-stream weights are applied to the
+            # whole shard here: same flops and bytes per token)
+            for b in dbl:
+                h_ = F.layer_norm(x, (hid,))
+                q, k, v = F.linear(h_, b["qkv"]).view(1, s, 3, H, D).unbind(2)
+                x = x + F.linear(attn(q, k, v), b["proj"])
+                x = x + F.linear(F.gelu(F.linear(F.layer_norm(x, (hid,)), b["up"]), approximate="tanh"), b["down"])
+            for b in sgl:
+                h_ = F.linear(F.layer_norm(x, (hid,)), b["l1"])
+                q, k, v = h_[..., : 3 * hid].view(1, s, 3, H, D).unbind(2)
+                x = x + F.linear(torch.cat([attn(q, k, v), F.gelu(h_[..., 3 * hid:], approximate="tanh")], -1), b["l2"])
+            return x
+    else:
+        ffn, txt_len, txt_dim = 13824, 512, 4096
+        ctx = torch.randn(1, txt_len, txt_dim, device=device, generator=g).to(bf)
+        blocks = [dict(q=lin(hid, hid), k=lin(hid, hid), v=lin(hid, hid), o=lin(hid, hid), cq=lin(hid, hid),
+                       ck=lin(txt_dim, hid), cv=lin(txt_dim, hid), co=lin(hid, hid), up=lin(hid, ffn),
+                       down=lin(ffn, hid)) for _ in range(40)]
+
+        def forward(x):
+            for b in blocks:
+                h_ = F.layer_norm(x, (hid,))
+                q, k, v = (F.linear(h_, b[n]).view(1, s, H, D) for n in ("q", "k", "v"))
+                x = x + F.linear(attn(q, k, v), b["o"])
+                h_ = F.layer_norm(x, (hid,))
+                cq = F.linear(h_, b["cq"]).view(1, s, H, D).transpose(1, 2)
+                ck = F.linear(ctx, b["ck"]).view(1, txt_len, H, D).transpose(1, 2)
+                cv = F.linear(ctx, b["cv"]).view(1, txt_len, H, D).transpose(1, 2)
+                x = x + F.linear(xdit_b200.attention(cq, ck, cv).transpose(1, 2).reshape(1, s, hid), b["co"])
+                x = x + F.linear(F.gelu(F.linear(F.layer_norm(x, (hid,)), b["up"]), approximate="tanh"), b["down"])
+            return x
+
+    with torch.no_grad():
+        for _ in range(2):
+            forward(x)
+        times = []
+        for _ in range(reps):
+            torch.cuda.synchronize(device)
+            if world > 1:
+                dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); forward(x); e1.record()
+            torch.cuda.synchronize(device)
+            times.append(e0.elapsed_time(e1))
+    times.sort()
+    ms = times[len(times) // 2]
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return {"ms_per_step": ms, "ulysses": U, "ring": R, "reps": reps,
+            "what": "one forward of a random-init stand-in (torch bf16 linears/norms/RoPE + xdit_b200 attention)"}
+
+
 def cpu_baseline(w):
     import torch
 
@@ -360,6 +461,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary workload and the CPU baseline")
     ap.add_argument("--layers", type=int, default=0, help="time only this many layers per step (profiling aid)")
+    ap.add_argument("--dit", default="flux", choices=["none", "flux", "wan", "both"],
+                    help="also time one DiT forward of a random-init stand-in of this architecture (extra.dit_step)")
     ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
                     help="replay the step as a CUDA graph (auto: only when N > 1, where the step is launch-bound)")
     args = ap.parse_args()
@@ -422,6 +525,15 @@ def main():
                 extra["hbm_kernels"] = hbm_kernels(torch, ops, device, hbm_peak, peak_kind)
             except Exception as e:
                 extra["hbm_kernels"] = {"error": repr(e)[:200]}
+        if args.dit != "none":
+            extra["dit_step"] = {}
+            for kind in (("flux", "wan") if args.dit == "both" else (args.dit,)):
+                try:
+                    extra["dit_step"][kind] = dit_step_latency(torch, dist, xdit_b200, kind, device, rank, world,
+                                                               reps=5 if kind == "flux" else 3)
+                except Exception as e:
+                    extra["dit_step"][kind] = {"error": repr(e)[:200]}
+                torch.cuda.empty_cache()
 
     if rank == 0:
         calls = w["layers"]
