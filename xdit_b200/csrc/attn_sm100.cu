@@ -199,6 +199,13 @@ __device__ __forceinline__ float ex2(float x) {
 #define XDIT_TRACE(role, it, ev) do {} while (0)
 #define XDIT_TRACE_DEP(role, it, ev, dep) do {} while (0)
 #endif
+// same instruction, but volatile: the compiler keeps a run of these in program order, which is how
+// the softmax loop forces a batch of independent ex2 to be issued back to back
+__device__ __forceinline__ float ex2_ordered(float x) {
+  float y;
+  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ float max3(float a, float b, float c) {
 #ifdef XDIT_EXP_MAX2
   return fmaxf(a, fmaxf(b, c));
@@ -618,6 +625,57 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_sm100_kernel(const __gri
       // polynomial on the FMA pipe and the rest through ex2 on the special-function unit.
       // P is handed to the tensor core in two halves of 64 key columns.
       const uint64_t sl2_2 = f2_pack(sl2, sl2), negm_2 = f2_pack(-m_run, -m_run);
+#if XDIT_EMU_PAIRS == 0
+      // Software-pipelined in blocks of 16 columns: the 16 ex2 of block b+1 are issued before the
+      // results of block b are consumed.  A warp issues in order, so without this every pair
+      // would wait out the special-function unit's latency before the next one starts.
+      uint64_t acc4[4] = {f2_pack(0.f, 0.f), f2_pack(0.f, 0.f), f2_pack(0.f, 0.f), f2_pack(0.f, 0.f)};
+      uint32_t pk[64];
+      float pcur[16], pnext[16];
+      auto stage_ab = [&](int blk, float* p) {
+        uint64_t x2[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          x2[i] = f2_fma(f2_pack(__uint_as_float(s[16 * blk + 2 * i]), __uint_as_float(s[16 * blk + 2 * i + 1])),
+                         sl2_2, negm_2);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          float x0, x1;
+          f2_unpack(x2[i], x0, x1);
+          p[2 * i] = ex2_ordered(x0);
+          p[2 * i + 1] = ex2_ordered(x1);
+        }
+      };
+      auto stage_c = [&](int blk, const float* p) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          acc4[i & 3] = f2_add(acc4[i & 3], f2_pack(p[2 * i], p[2 * i + 1]));
+          pk[8 * blk + i] = pack2<BF16>(p[2 * i], p[2 * i + 1]);
+        }
+      };
+      stage_ab(0, pcur);
+#pragma unroll
+      for (int blk = 0; blk < 8; ++blk) {
+        if (blk + 1 < 8) stage_ab(blk + 1, pnext);
+        stage_c(blk, pcur);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) pcur[i] = pnext[i];
+        if (blk == 3 || blk == 7) {
+          const int half = blk >> 2;
+          if (half == 0) XDIT_TRACE_DEP(t, j, 3, pk[0] ^ pk[31]);
+          XDIT_TMEM_ST32(pk, 32 * half, tmem_s + 32 * half);
+          tmem_wait_st();
+          tc_fence_before();
+          mbar_arrive(bar_p_full(t, half));
+          if (half == 0) XDIT_TRACE(t, j, 4);
+        }
+      }
+      {
+        float a0, a1;
+        f2_unpack(f2_add(f2_add(acc4[0], acc4[1]), f2_add(acc4[2], acc4[3])), a0, a1);
+        l_run += a0 + a1;
+      }
+#else
       uint64_t sum_a = f2_pack(0.f, 0.f), sum_b = sum_a;
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
@@ -654,6 +712,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_sm100_kernel(const __gri
         f2_unpack(f2_add(sum_a, sum_b), a0, a1);
         l_run += a0 + a1;
       }
+#endif
       XDIT_TRACE(t, j, 5);
       return true;
     };
