@@ -14,7 +14,9 @@ is the same metric through ``xdit_b200.USP`` with the step's inputs in pinned ho
 the results read back, copies inside the timed region.
 
 N > 1 is launched by ``torch.distributed.run`` (one rank per GPU, NCCL); the sequence is sharded
-over N ranks (strong scaling): Flux uses Ulysses degree N, Wan uses ring x Ulysses.
+over N ranks (strong scaling) with Ulysses degree N, which is the fastest split behind NVSwitch
+(measured at 8 GPUs on the 75.6K workload: U8 7755, U4xR2 7438, U2xR4 6872, R8 6046 TFLOP/s);
+``--sp ULYSSESxRING`` selects another split, e.g. ``--sp 2x4`` for BASELINE config 3's degrees.
 
 ``--impl reference`` times the CPU restatement of the reference's algorithm (the oracle) on the
 host cores of rank 0, on a bounded sample (a subset of heads) of the same workload.
@@ -37,7 +39,7 @@ WORKLOADS = {
     "flux": dict(desc="Flux.1-dev 1024x1024 MMDiT self-attention: 57 layers x (24 heads x 128, 512 text + 4096 image tokens)",
                  layers=57, sets=57, H=24, D=128, S=4608, degrees={1: (1, 1), 2: (2, 1), 4: (4, 1), 8: (8, 1)}),
     "wan": dict(desc="Wan2.1-14B 81f 720x1280 self-attention: 40 layers x (40 heads x 128, 75,600 tokens)",
-                layers=40, sets=2, H=40, D=128, S=75600, degrees={1: (1, 1), 2: (1, 2), 4: (2, 2), 8: (2, 4)}),
+                layers=40, sets=2, H=40, D=128, S=75600, degrees={1: (1, 1), 2: (2, 1), 4: (4, 1), 8: (8, 1)}),
 }
 
 
@@ -204,6 +206,9 @@ def timed_region(torch, dist, fn, steps, warmup, device, multi):
 
 def run_workload(torch, dist, xdit_b200, ops, name, w, args, device, rank, world, layers, with_e2e):
     U, R = w["degrees"][world]
+    if getattr(args, "sp", None):
+        U, R = (int(x) for x in args.sp.lower().split("x"))
+        assert U * R == world, "--sp UxR must multiply to the number of GPUs"
     xdit_b200.init_sequence_parallel(U, R)
     P = U * R
     S = w["S"]
@@ -463,6 +468,8 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="time only this many layers per step (profiling aid)")
     ap.add_argument("--dit", default="flux", choices=["none", "flux", "wan", "both"],
                     help="also time one DiT forward of a random-init stand-in of this architecture (extra.dit_step)")
+    ap.add_argument("--sp", default=None, help="override the sequence-parallel degrees of the main workload: ULYSSESxRING, e.g. 2x4")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end (host buffers) leg")
     ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
                     help="replay the step as a CUDA graph (auto: only when N > 1, where the step is launch-bound)")
     args = ap.parse_args()
@@ -502,12 +509,13 @@ def main():
     tf_peak, hbm_peak, peak_kind = peaks()
     if args.layers > 0:
         w = dict(w, layers=min(args.layers, w["layers"]))
-    main_res = run_workload(torch, dist, xdit_b200, ops, name, w, args, device, rank, world, w["layers"], True)
+    main_res = run_workload(torch, dist, xdit_b200, ops, name, w, args, device, rank, world, w["layers"],
+                            not args.no_e2e)
     extra = {}
     if not args.no_extra:
         other = "wan" if name == "flux" else "flux"
         wo = WORKLOADS[other]
-        a2 = argparse.Namespace(steps=max(1, min(args.steps, 3)), warmup=3, graph=args.graph)
+        a2 = argparse.Namespace(steps=max(1, min(args.steps, 3)), warmup=3, graph=args.graph, sp=None)
         layers = 4 if other == "wan" else wo["layers"]
         try:
             r2 = run_workload(torch, dist, xdit_b200, ops, other, wo, a2, device, rank, world, layers, False)
@@ -558,7 +566,7 @@ def main():
                 "unit": "TFLOP/s", "frac": per_gpu_tf / tf_peak, "peak_kind": f"of {peak_kind} (cuBLAS bf16 burst)",
                 "avg_call_ms": kernel_ms, "traffic": None,
             },
-            "e2e": main_res["e2e"],
+            "e2e": main_res.get("e2e"),
             "clocks": main_res["clocks"],
             "gpu_launches": main_res["launches"],
             "extra": extra,

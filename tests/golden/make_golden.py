@@ -306,6 +306,64 @@ def _cache_cases(outdir):
     np.savez_compressed(os.path.join(outdir, "kvcache_sp.npz"), **rec)
 
 
+# --------------------------------------------------------------------------------------
+# USP with the PipeFusion stale-KV buffer under Ulysses (usp.py:313-314 -> cache_manager.py:138-194)
+# --------------------------------------------------------------------------------------
+def _usp_kvcache_worker(rank, world, port, outdir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(1)
+    usp, backend, cache, rts = import_reference()
+    import xfuser.core.distributed as xd
+
+    U, R, B, H, D = 2, 1, 1, 4, 16
+    s_loc, patches = 32, [16, 16]
+    pg = dist.new_group(list(range(world)), backend="gloo")
+
+    class PG:
+        ULYSSES_PG = pg
+        RING_PG = None
+
+    usp.PROCESS_GROUP = PG
+    usp.get_ulysses_parallel_world_size = lambda: U
+    usp.get_ulysses_parallel_rank = lambda: rank
+    usp.get_ring_parallel_world_size = lambda: R
+    usp.get_sequence_parallel_world_size = lambda: U * R
+    state = FakeRuntimeState(backend.AttentionBackendType.SDPA)
+    state.num_pipeline_patch = len(patches)
+    state.pp_patches_token_num = patches
+    state.pp_patches_token_start_idx_local = [0, 16, 32]
+    usp.get_runtime_state = lambda: state
+    xd.get_runtime_state = lambda: state
+    xd.get_ulysses_parallel_world_size = lambda: U
+    cache.runtime_state_is_initialized = lambda: True
+    layer = "L"
+    cache.get_cache_manager().register_cache_entry(layer, "attn", "sequence_parallel_attn_cache")
+
+    g = torch.Generator().manual_seed(1234)
+    mk = lambda n: torch.randn(B, H, U * n, D, generator=g)
+    q0, k0, v0 = mk(s_loc), mk(s_loc), mk(s_loc)          # warm-up step: full local sequences
+    q1, k1, v1 = mk(16), mk(16), mk(16)                   # patch step: fresh rows of patch 1
+    sh = lambda t: t.chunk(U, dim=2)[rank]
+    state.patch_mode = False
+    out0 = usp.USP(sh(q0), sh(k0), sh(v0), attn_layer=layer)
+    state.patch_mode = True
+    state.pipeline_patch_idx = 1
+    out1 = usp.USP(sh(q1), sh(k1), sh(v1), attn_layer=layer)
+    outs = []
+    for o in (out0, out1):
+        gathered = [torch.empty_like(o) for _ in range(world)]
+        dist.all_gather(gathered, o.contiguous())
+        outs.append(np.stack([x.numpy() for x in gathered]))
+    if rank == 0:
+        np.savez_compressed(os.path.join(outdir, "uspkv_u2r1.npz"), q0=q0.numpy(), k0=k0.numpy(), v0=v0.numpy(),
+                            q1=q1.numpy(), k1=k1.numpy(), v1=v1.numpy(), out0=outs[0], out1=outs[1],
+                            patches=np.array(patches), patch_idx=np.array(1), U=np.array(U))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def main():
     outdir = HERE
     port = 29611
@@ -315,6 +373,7 @@ def main():
             continue
         mp.spawn(_usp_worker, args=(world, port, cases, outdir), nprocs=world, join=True)
         port += 1
+    mp.spawn(_usp_kvcache_worker, args=(2, port, outdir), nprocs=2, join=True)
     _layout_cases(outdir)
     _cache_cases(outdir)
     print("golden fixtures written to", outdir)

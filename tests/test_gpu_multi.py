@@ -4,7 +4,9 @@ fp32 inputs take the CUDA-core kernel (tight tolerance); bf16 inputs take the tc
 import pytest
 import torch
 
-from tests.usp_worker import golden_files, run
+import os
+
+from tests.usp_worker import HERE, golden_files, run, run_kv
 
 pytestmark = pytest.mark.gpu
 
@@ -25,3 +27,9 @@ def test_two_gpus(mode, dtype, tol):
 def test_four_gpus(mode, dtype, tol):
     _need(4)
     run(4, golden_files(4), mode, 29760, backend="nccl", dtype_name=dtype, tol=tol)
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 5e-5), ("bfloat16", 3e-2)])
+def test_stale_kv_under_ulysses_two_gpus(dtype, tol):
+    _need(2)
+    run_kv(2, os.path.join(HERE, "golden", "uspkv_u2r1.npz"), 29770, backend="nccl", dtype_name=dtype, tol=tol)

@@ -5,7 +5,9 @@ the kernels themselves are checked on the GPU (tests marked gpu).  Expected valu
 outputs of the unmodified reference (tests/golden)."""
 import pytest
 
-from tests.usp_worker import golden_files, run
+import os
+
+from tests.usp_worker import HERE, golden_files, run, run_kv
 
 
 @pytest.mark.parametrize("mode", ["usp", "legacy", "compat"])
@@ -16,3 +18,9 @@ def test_world2_matches_reference(mode):
 @pytest.mark.parametrize("mode", ["usp", "legacy"])
 def test_world4_matches_reference(mode):
     run(4, golden_files(4), mode, 29730 + ["usp", "legacy"].index(mode))
+
+
+def test_stale_kv_under_ulysses_matches_reference():
+    """USP(attn_layer=...) with PipeFusion patches and Ulysses degree 2: the fresh rows reach the cache
+    manager as two segments of the all-to-all receive buffer."""
+    run_kv(2, os.path.join(HERE, "golden", "uspkv_u2r1.npz"), 29741)

@@ -165,3 +165,32 @@ def test_causal_ring_equals_dense_causal():
     t = lambda x: np.transpose(x, (0, 2, 1, 3))
     dense, _ = O.attention_dense(t(q), t(k), t(v), causal=True)
     np.testing.assert_allclose(np.concatenate(outs, axis=1), t(dense), atol=1e-12)
+
+
+def test_usp_with_stale_kv_under_ulysses(golden_dir):
+    """USP(attn_layer=...) with two PipeFusion patches and Ulysses degree 2 (usp.py:313-314 ->
+    cache_manager.py:138-194): warm-up step, then a patch step that refreshes patch 1 only."""
+    z = np.load(os.path.join(golden_dir, "uspkv_u2r1.npz"))
+    U = int(z["U"])
+    patches = [int(x) for x in z["patches"]]
+    starts = [0]
+    for n in patches:
+        starts.append(starts[-1] + n)
+    t = lambda x: np.transpose(x, (0, 2, 1, 3))
+    caches = [O.KVCacheOracle("sp", U=U) for _ in range(U)]
+
+    def step(q, k, v, patch_mode, patch_idx):
+        sh = lambda x: np.array_split(x, U, axis=2)
+        qs, ks, vs = O.input_all_to_all(sh(q)), O.input_all_to_all(sh(k)), O.input_all_to_all(sh(v))
+        outs = []
+        for r in range(U):
+            kc, vc = caches[r].update(t(ks[r]), t(vs[r]), 1, len(patches), patch_mode, patch_idx, starts, patches)
+            o, _ = O.attention_dense(qs[r], t(kc), t(vc))
+            outs.append(o)
+        return O.output_all_to_all(outs)
+
+    out0 = step(z["q0"], z["k0"], z["v0"], False, 0)
+    out1 = step(z["q1"], z["k1"], z["v1"], True, int(z["patch_idx"]))
+    for r in range(U):
+        np.testing.assert_allclose(out0[r], z["out0"][r], atol=2e-5, rtol=1e-4)
+        np.testing.assert_allclose(out1[r], z["out1"][r], atol=2e-5, rtol=1e-4)

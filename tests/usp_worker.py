@@ -92,6 +92,81 @@ def worker(rank, world, port, files, mode, errq, backend="gloo", dtype_name="flo
         raise
 
 
+def kv_worker(rank, world, port, path, errq, backend="gloo", dtype_name="float32", tol=5e-5):
+    """USP with the PipeFusion stale-KV buffer under Ulysses: warm-up step, then a patch step."""
+    try:
+        sys.path.insert(0, ROOT)
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        gpu = backend == "nccl"
+        if gpu:
+            torch.cuda.set_device(rank)
+            dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        else:
+            dist.init_process_group("gloo", rank=rank, world_size=world)
+            torch.set_num_threads(1)
+        import xdit_b200
+
+        if not gpu:
+            from tests import fake_ops
+
+            fake_ops.install()
+        z = np.load(path)
+        U = int(z["U"])
+        dtype = getattr(torch, dtype_name)
+        dev = torch.device("cuda", rank) if gpu else torch.device("cpu")
+        put = lambda a: torch.from_numpy(a).to(dtype).to(dev).chunk(U, dim=2)[rank]
+        xdit_b200.init_sequence_parallel(U, 1, backend=backend)
+        rs = xdit_b200.initialize_runtime_state()
+        rs.set_patches([int(x) for x in z["patches"]])
+        layer = "L"
+        xdit_b200.get_cache_manager().register_cache_entry(layer, "attn", "sequence_parallel_attn_cache")
+        rs.set_patched_mode(False)
+        out0 = xdit_b200.USP(put(z["q0"]), put(z["k0"]), put(z["v0"]), attn_layer=layer)
+        rs.set_patched_mode(True)
+        rs.pipeline_patch_idx = int(z["patch_idx"])
+        out1 = xdit_b200.USP(put(z["q1"]), put(z["k1"]), put(z["v1"]), attn_layer=layer)
+        if gpu:
+            torch.cuda.synchronize()
+            from xdit_b200 import ops
+
+            ops.check_status()
+        for got, name in ((out0, "out0"), (out1, "out1")):
+            ref = torch.from_numpy(z[name][rank]).double()
+            assert tuple(got.shape) == tuple(ref.shape), (name, got.shape, ref.shape)
+            err = (got.detach().double().cpu() - ref).abs().max().item()
+            assert err < tol, (name, rank, err)
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception as e:
+        import traceback
+
+        errq.put(f"rank {rank}: {e}\n{traceback.format_exc()}")
+        raise
+
+
+def run_kv(world, path, port, **kw):
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    errq = ctx.SimpleQueue()
+    procs = [ctx.Process(target=kv_worker, args=(r, world, port, path, errq), kwargs=kw) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(600)
+    msgs = []
+    while not errq.empty():
+        msgs.append(errq.get())
+    alive = [p for p in procs if p.is_alive()]
+    for p in alive:
+        p.terminate()
+    assert not msgs, "\n".join(msgs)
+    assert not alive, "ranks did not finish"
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+
+
 def run(world, files, mode, port, **kw):
     import torch.multiprocessing as mp
 
