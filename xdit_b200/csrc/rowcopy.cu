@@ -2,10 +2,13 @@
 // PipeFusion stale-KV patch update.  A "row" is head_dim contiguous elements; the four outer
 // indices have independent byte strides on the source and on the destination side.
 //
-// Work decomposition: a unit is (job, i0, i1, i2, a run of kRowsPerUnit consecutive i3 rows).
-// The unit index is decomposed once per CTA iteration with scalar arithmetic; inside a unit the
-// threads move 16-byte vectors with four independent loads in flight per thread.  The grid is a
-// multiple of the SM count and grid-strides over units.
+// Work decomposition: a unit is (job, i0, a block of i1, i2, a run of kRowsPerUnit consecutive i3
+// rows).  The unit index is decomposed once per CTA iteration with scalar arithmetic; inside a
+// unit the threads move 16-byte vectors with four independent loads in flight per thread.  When
+// consecutive i1 (heads) are adjacent in memory on one side -- the [B,S,H,D] views the DiT
+// processors pass -- a unit takes several of them, so that the scattered side still moves in runs
+// of a few KB instead of single 256-byte rows.  The grid is a multiple of the SM count and
+// grid-strides over units.
 #include "common.cuh"
 
 namespace xdit {
@@ -14,9 +17,12 @@ namespace {
 constexpr int kRowsPerUnit = 64;
 constexpr int kThreads = 256;
 
+constexpr int kMaxBlock1 = 8;
+
 struct RowCopyArgs {
   RowCopyJob job[kMaxRowCopyJobs];
   int64_t unit_end[kMaxRowCopyJobs];  // exclusive prefix end of each job's units
+  int32_t blk1[kMaxRowCopyJobs];      // how many consecutive i1 a unit covers
   int32_t njobs;
 };
 
@@ -37,38 +43,46 @@ __global__ void __launch_bounds__(kThreads) row_copy_kernel(const __grid_constan
     const RowCopyJob& jb = args.job[j];
     int64_t u = unit - (j ? args.unit_end[j - 1] : 0);
     const int chunks = (jb.n[3] + kRowsPerUnit - 1) / kRowsPerUnit;
+    const int hb = args.blk1[j];
+    const int n1b = (jb.n[1] + hb - 1) / hb;
     const int c3 = (int)(u % chunks); u /= chunks;
     const int i2 = (int)(u % jb.n[2]); u /= jb.n[2];
-    const int i1 = (int)(u % jb.n[1]); u /= jb.n[1];
+    const int i1 = (int)(u % n1b) * hb; u /= n1b;
     const int i0 = (int)u;
     const int r0 = c3 * kRowsPerUnit;
     const int nrows = min(kRowsPerUnit, jb.n[3] - r0);
+    const uint32_t nhb = min(hb, jb.n[1] - i1);
     const char* s = jb.src + i0 * jb.s_stride[0] + i1 * jb.s_stride[1] + i2 * jb.s_stride[2] +
                     (int64_t)r0 * jb.s_stride[3];
     char* d = jb.dst + i0 * jb.d_stride[0] + i1 * jb.d_stride[1] + i2 * jb.d_stride[2] +
               (int64_t)r0 * jb.d_stride[3];
     const uint32_t vpr = jb.row_bytes / VEC;
-    const uint32_t nvec = nrows * vpr;
+    const uint32_t vpg = vpr * nhb;  // vectors per row group: nhb rows of adjacent i1
+    const uint32_t nvec = nrows * vpg;
     const int64_t ss = jb.s_stride[3], ds = jb.d_stride[3];
+    const int64_t ss1 = jb.s_stride[1], ds1 = jb.d_stride[1];
+    auto locate = [&](uint32_t e, int64_t& so, int64_t& dof) {
+      const uint32_t r = e / vpg, rem = e - r * vpg;
+      const uint32_t h = rem / vpr, c = rem - h * vpr;
+      so = r * ss + h * ss1 + (int64_t)c * VEC;
+      dof = r * ds + h * ds1 + (int64_t)c * VEC;
+    };
     uint32_t idx = threadIdx.x;
     for (; idx + 3 * kThreads < nvec; idx += 4 * kThreads) {
       V val[4];
-      uint32_t r[4], c[4];
+      int64_t so[4], dof[4];
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        const uint32_t e = idx + k * kThreads;
-        r[k] = e / vpr;
-        c[k] = e - r[k] * vpr;
-        val[k] = __ldg(reinterpret_cast<const V*>(s + r[k] * ss + (int64_t)c[k] * VEC));
+        locate(idx + k * kThreads, so[k], dof[k]);
+        val[k] = __ldg(reinterpret_cast<const V*>(s + so[k]));
       }
 #pragma unroll
-      for (int k = 0; k < 4; ++k)
-        *reinterpret_cast<V*>(d + r[k] * ds + (int64_t)c[k] * VEC) = val[k];
+      for (int k = 0; k < 4; ++k) *reinterpret_cast<V*>(d + dof[k]) = val[k];
     }
     for (; idx < nvec; idx += kThreads) {
-      const uint32_t r = idx / vpr, c = idx - r * vpr;
-      *reinterpret_cast<V*>(d + r * ds + (int64_t)c * VEC) =
-          __ldg(reinterpret_cast<const V*>(s + r * ss + (int64_t)c * VEC));
+      int64_t so, dof;
+      locate(idx, so, dof);
+      *reinterpret_cast<V*>(d + dof) = __ldg(reinterpret_cast<const V*>(s + so));
     }
   }
 }
@@ -98,8 +112,13 @@ int launch_row_copy(const RowCopyJob* jobs, int njobs, cudaStream_t stream) {
   int live = 0;
   for (int j = 0; j < njobs; ++j) {
     const RowCopyJob& jb = jobs[j];
-    int64_t units = 1;
-    for (int k = 0; k < 3; ++k) units *= jb.n[k];
+    // block consecutive i1 when they are adjacent in memory on either side
+    int hb = 1;
+    if (jb.n[1] > 1 && (jb.s_stride[1] == jb.row_bytes || jb.d_stride[1] == jb.row_bytes)) {
+      hb = jb.n[1] < kMaxBlock1 ? jb.n[1] : kMaxBlock1;
+      while (hb > 1 && (int64_t)hb * jb.row_bytes > 4096) hb >>= 1;  // keep runs around 2-4 KB
+    }
+    int64_t units = (int64_t)jb.n[0] * ((jb.n[1] + hb - 1) / hb) * jb.n[2];
     units *= (jb.n[3] + kRowsPerUnit - 1) / kRowsPerUnit;
     if (units <= 0 || jb.row_bytes <= 0) continue;  // empty job: nothing to move
     if (!jb.src || !jb.dst) {
@@ -108,6 +127,7 @@ int launch_row_copy(const RowCopyJob* jobs, int njobs, cudaStream_t stream) {
     }
     total += units;
     args.job[live] = jb;
+    args.blk1[live] = hb;
     args.unit_end[live] = total;
     ++live;
   }
@@ -117,12 +137,7 @@ int launch_row_copy(const RowCopyJob* jobs, int njobs, cudaStream_t stream) {
   int rc = check_device(&sms);
   if (rc) return rc;
   const int vec = pick_vec(args.job, live);
-  if ((args.job[0].row_bytes & 1) != 0) {
-    set_error("row copy: odd row size");
-    return XDIT_E_ALIGN;
-  }
-  int64_t want = (total + 0) ;
-  int grid = (int)((want < (int64_t)sms * 8) ? want : (int64_t)sms * 8);
+  int grid = (int)((total < (int64_t)sms * 8) ? total : (int64_t)sms * 8);
   if (grid < 1) grid = 1;
   switch (vec) {
     case 16: row_copy_kernel<16><<<grid, kThreads, 0, stream>>>(args); break;
