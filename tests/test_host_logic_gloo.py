@@ -10,14 +10,46 @@ import os
 from tests.usp_worker import HERE, golden_files, run, run_kv
 
 
-@pytest.mark.parametrize("mode", ["usp", "legacy", "compat"])
+@pytest.mark.parametrize("mode", ["usp", "legacy", "compat", "yunchang"])
 def test_world2_matches_reference(mode):
-    run(2, golden_files(2), mode, 29720 + ["usp", "legacy", "compat"].index(mode))
+    run(2, golden_files(2), mode, 29720 + ["usp", "legacy", "compat", "yunchang"].index(mode))
 
 
-@pytest.mark.parametrize("mode", ["usp", "legacy"])
+@pytest.mark.parametrize("mode", ["usp", "legacy", "yunchang"])
 def test_world4_matches_reference(mode):
-    run(4, golden_files(4), mode, 29730 + ["usp", "legacy"].index(mode))
+    run(4, golden_files(4), mode, 29730 + ["usp", "legacy", "yunchang"].index(mode))
+
+
+def test_yunchang_shim_serves_the_names_the_reference_imports():
+    """xfuser/envs.py:346-352 and the other import sites listed in xdit_b200/yunchang_compat.py."""
+    import sys
+
+    from xdit_b200 import yunchang_compat
+
+    assert "yunchang" not in sys.modules or getattr(sys.modules["yunchang"], "__xdit_b200_shim__", False)
+    assert yunchang_compat.install()
+    try:
+        from yunchang import (LongContextAttention, LongContextAttentionQKVPacked, UlyssesAttention,  # noqa: F401
+                              ring_flash_attn_func, set_seq_parallel_pg)
+        from yunchang.comm.all_to_all import SeqAllToAll4D  # noqa: F401
+        from yunchang.globals import HAS_SPARSE_SAGE_ATTENTION, PROCESS_GROUP
+        from yunchang.kernels import AttnType, select_flash_attn_impl
+        from yunchang.ring.ring_flash_attn import RingFlashAttnFunc, ring_flash_attn_backward  # noqa: F401
+        from yunchang.ring.utils import RingComm, update_out_and_lse  # noqa: F401
+        import xdit_b200
+
+        assert PROCESS_GROUP is xdit_b200.PROCESS_GROUP and AttnType is xdit_b200.AttnType
+        assert HAS_SPARSE_SAGE_ATTENTION is False
+        assert AttnType.from_string("fa") is AttnType.FA
+        with pytest.raises(NotImplementedError):
+            select_flash_attn_impl(AttnType.FA, stage="bwd-only")
+        with pytest.raises(NotImplementedError):
+            ring_flash_attn_backward()
+        layer = LongContextAttention(use_pack_qkv=True)
+        assert layer.scatter_idx == 2 and layer.gather_idx == 1 and layer.use_pack_qkv
+    finally:
+        yunchang_compat.uninstall()
+    assert "yunchang" not in sys.modules
 
 
 def test_stale_kv_under_ulysses_matches_reference():

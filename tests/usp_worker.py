@@ -66,6 +66,8 @@ def worker(rank, world, port, files, mode, errq, backend="gloo", dtype_name="flo
 
                 register_attention_function(AttentionBackendType.SAGE)(_custom)
                 out = xdit_b200.USP(ql, kl, vl, backend=AttentionBackendType.SAGE, combine_qkv_a2a=True, **kw)
+            elif mode == "yunchang":
+                out = _yunchang_shaped_forward(xdit_b200, ql, kl, vl, kw, strat, rank, U, R, dev)
             else:  # legacy [B,S,H,D] layer
                 layer = xdit_b200.xFuserLongContextAttention()
                 t = lambda x: x.transpose(1, 2)
@@ -90,6 +92,47 @@ def worker(rank, world, port, files, mode, errq, backend="gloo", dtype_name="flo
 
         errq.put(f"rank {rank}: {e}\n{traceback.format_exc()}")
         raise
+
+
+def _yunchang_shaped_forward(xdit_b200, ql, kl, vl, kw, strat, rank, U, R, dev):
+    """The [B,S,H,D] layer's forward spelled with the yunchang-named pieces, in the order of the
+    reference's ``hybrid/attn_layer.py:136-236``: joint-Q concat, joint K/V head slice, SeqAllToAll4D
+    (heads scattered, sequence gathered), ring function, inverse SeqAllToAll4D.  Also sends a token
+    around the ring with RingComm and, without joint tensors, runs the shim's LongContextAttention."""
+    from xdit_b200 import yunchang_compat
+
+    assert yunchang_compat.install()
+    from yunchang import LongContextAttention
+    from yunchang.comm.all_to_all import SeqAllToAll4D
+    from yunchang.globals import PROCESS_GROUP
+    from yunchang.ring.utils import RingComm
+
+    t = lambda x: x.transpose(1, 2)
+    q, k, v = t(ql), t(kl), t(vl)
+    u_rank = rank % U
+    jk = jv = None
+    if strat:
+        jq, jk, jv = (t(kw[n]) for n in ("joint_query", "joint_key", "joint_value"))
+        q = torch.cat([q, jq], 1) if strat == "rear" else torch.cat([jq, q], 1)
+        hl = jk.shape[2] // U
+        jk, jv = jk[:, :, u_rank * hl:(u_rank + 1) * hl], jv[:, :, u_rank * hl:(u_rank + 1) * hl]
+    q2, k2, v2 = (SeqAllToAll4D.apply(PROCESS_GROUP.ULYSSES_PG, x, 2, 1) for x in (q, k, v))
+    ctx = xdit_b200.xdit_ring_flash_attn_func(
+        q2, k2, v2, group=PROCESS_GROUP.RING_PG, joint_tensor_key=jk, joint_tensor_value=jv,
+        joint_strategy=strat or "none")
+    out = t(SeqAllToAll4D.apply(PROCESS_GROUP.ULYSSES_PG, ctx, 1, 2))
+    if R > 1:
+        comm = RingComm(PROCESS_GROUP.RING_PG)
+        token = torch.full((4,), float(rank), device=dev)
+        got = comm.send_recv(token)
+        comm.commit()
+        comm.wait()
+        prev = ((rank // U - 1) % R) * U + u_rank
+        assert torch.equal(got.cpu(), torch.full((4,), float(prev))), (rank, got)
+    if not strat:
+        out_layer = t(LongContextAttention()(t(ql), t(kl), t(vl)))
+        assert (out_layer.double() - out.double()).abs().max().item() < 1e-2
+    return out
 
 
 def kv_worker(rank, world, port, path, errq, backend="gloo", dtype_name="float32", tol=5e-5):

@@ -93,12 +93,33 @@ def concat_joint_tensors_decorator(func):
     return wrapper
 
 
-def _sdpa_all_to_all_single(x):
+def _sdpa_all_to_all_single(x, group=None):
     """Equal-split all-to-all of ``x`` viewed flat over the Ulysses group (``usp.py:87-93``)."""
     flat = x.reshape(-1)
     out = torch.empty_like(flat)
-    dist.all_to_all_single(out, flat, group=PROCESS_GROUP.ULYSSES_PG)
+    dist.all_to_all_single(out, flat, group=PROCESS_GROUP.ULYSSES_PG if group is None else group)
     return out.reshape(x.shape)
+
+
+def _input_all_to_all(x, U, group=None):
+    """Heads scattered, sequence gathered: [B,H,s,D] -> [B,H/U,U*s,D] over ``group``."""
+    assert x.ndim == 4, "x must have 4 dimensions, got {}".format(x.ndim)
+    b, h, s, d = x.shape
+    assert h % U == 0, "h must be divisible by world_size, got {} and {}".format(h, U)
+    send = torch.empty(h * b * s * d, dtype=x.dtype, device=x.device)
+    ops.ulysses_pack([dict(src=x, dst=send, peer_stride=(h // U) * b * s * d)], U)
+    recv = _sdpa_all_to_all_single(send, group)
+    return ops.ulysses_unpack_in(recv, b, h // U, s, d, U)
+
+
+def _output_all_to_all(x, U, group=None):
+    """Sequence scattered, heads gathered: [B,H/U,S',D] -> [B,H,S'/U,D] over ``group``."""
+    assert x.ndim == 4, "x must have 4 dimensions, got {}".format(x.ndim)
+    b, h, s, d = x.shape
+    assert s % U == 0, "s must be divisible by world_size, got {} and {}".format(s, U)
+    send = ops.ulysses_pack_out(x)
+    recv = _sdpa_all_to_all_single(send, group)
+    return ops.ulysses_unpack_out(recv, b, h, s // U, d, U)
 
 
 def _ft_c_input_all_to_all(x):
@@ -106,13 +127,7 @@ def _ft_c_input_all_to_all(x):
     U = get_ulysses_parallel_world_size()
     if U <= 1:
         return x
-    assert x.ndim == 4, "x must have 4 dimensions, got {}".format(x.ndim)
-    b, h, s, d = x.shape
-    assert h % U == 0, "h must be divisible by world_size, got {} and {}".format(h, U)
-    send = torch.empty(h * b * s * d, dtype=x.dtype, device=x.device)
-    ops.ulysses_pack([dict(src=x, dst=send, peer_stride=(h // U) * b * s * d)], U)
-    recv = _sdpa_all_to_all_single(send)
-    return ops.ulysses_unpack_in(recv, b, h // U, s, d, U)
+    return _input_all_to_all(x, U)
 
 
 def _combined_qkv_all_to_all(q, k, v):
@@ -139,12 +154,7 @@ def _ft_c_output_all_to_all(x):
     U = get_ulysses_parallel_world_size()
     if U <= 1:
         return x
-    assert x.ndim == 4, "x must have 4 dimensions, got {}".format(x.ndim)
-    b, h, s, d = x.shape
-    assert s % U == 0, "s must be divisible by world_size, got {} and {}".format(s, U)
-    send = ops.ulysses_pack_out(x)
-    recv = _sdpa_all_to_all_single(send)
-    return ops.ulysses_unpack_out(recv, b, h, s // U, d, U)
+    return _output_all_to_all(x, U)
 
 
 def _update_and_get_kv_cache(key, value, attn_layer):
