@@ -46,7 +46,7 @@ constexpr int kTile = 128;
 constexpr int kThreads = 384;  // 8 softmax warps, MMA warp, TMA warp, 2 idle warps (full register-trading warpgroup)
 constexpr int kSlabBytes = kTile * 128;       // one 64-element slab of a 128-row tile
 constexpr int kBoxBytes = kChunk * 128;       // one TMA box: 64 rows x 64 elements
-constexpr uint64_t kWaitLimitNs = 200000000ull;  // 0.2 s: no legitimate wait comes near this
+constexpr uint32_t kWaitLimitNs = 200000000u;  // 0.2 s: no legitimate wait comes near this
 #ifndef XDIT_EMU_PAIRS
 #define XDIT_EMU_PAIRS 0
 #endif
@@ -96,16 +96,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
-__device__ __forceinline__ uint64_t global_timer_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+// low word of the nanosecond timer: differences are exact up to 4.29 s, far above the wait limit
+__device__ __forceinline__ uint32_t global_timer_ns() {
+  uint32_t t;
+  asm volatile("mov.u32 %0, %%globaltimer_lo;" : "=r"(t));
   return t;
 }
 // Bounded wait.  Returns false when the CTA is aborting or the time limit passed (and then
 // raises the abort flag itself, recording `code`).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
   if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = global_timer_ns();
+  const uint32_t t0 = global_timer_ns();
   for (uint32_t it = 0;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
@@ -143,6 +144,59 @@ __device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
       ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(acc) : "memory");
+}
+// One lane of a converged warp.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
+// Groups of MMAs in one asm block.  A shared-memory descriptor is its tile's base descriptor plus a
+// constant in the low word (the address field counts 16-byte units; shared-memory addresses stay
+// below its 256 KB range) over a common high word, so a step costs two adds and the MMA.
+// S = Q K^T at head_dim 128: 8 k-steps, both operands K-major tiles of 128 rows (16 KB slabs).
+__device__ __forceinline__ void qk_block8(uint32_t d_tmem, uint32_t q_lo, uint32_t k_lo, uint32_t hi, uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred pt, pf;\n\t.reg .b32 ta, tb;\n\t.reg .b64 da, db;\n\t"
+      "setp.eq.u32 pt, %3, %3;\n\tsetp.ne.u32 pf, %3, %3;\n\t"
+      "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, pf;\n\t"
+      "add.u32 ta, %1, %5;\n\tadd.u32 tb, %2, %5;\n\tmov.b64 da, {ta, %3};\n\tmov.b64 db, {tb, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, pt;\n\t"
+      "add.u32 ta, %1, %6;\n\tadd.u32 tb, %2, %6;\n\tmov.b64 da, {ta, %3};\n\tmov.b64 db, {tb, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, pt;\n\t"
+      "add.u32 ta, %1, %7;\n\tadd.u32 tb, %2, %7;\n\tmov.b64 da, {ta, %3};\n\tmov.b64 db, {tb, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, pt;\n\t"
+      "add.u32 ta, %1, %8;\n\tadd.u32 tb, %2, %8;\n\tmov.b64 da, {ta, %3};\n\tmov.b64 db, {tb, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, pt;\n\t"
+      "add.u32 ta, %1, %9;\n\tadd.u32 tb, %2, %9;\n\tmov.b64 da, {ta, %3};\n\tmov.b64 db, {tb, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, pt;\n\t"
+      "add.u32 ta, %1, %10;\n\tadd.u32 tb, %2, %10;\n\tmov.b64 da, {ta, %3};\n\tmov.b64 db, {tb, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, pt;\n\t"
+      "add.u32 ta, %1, %11;\n\tadd.u32 tb, %2, %11;\n\tmov.b64 da, {ta, %3};\n\tmov.b64 db, {tb, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, pt;\n\t"
+      "}"
+      ::"r"(d_tmem), "r"(q_lo), "r"(k_lo), "r"(hi), "r"(idesc),
+        "n"(((1 >> 2) * (128 * 128) + (1 & 3) * 32) >> 4), "n"(((2 >> 2) * (128 * 128) + (2 & 3) * 32) >> 4), "n"(((3 >> 2) * (128 * 128) + (3 & 3) * 32) >> 4), "n"(((4 >> 2) * (128 * 128) + (4 & 3) * 32) >> 4), "n"(((5 >> 2) * (128 * 128) + (5 & 3) * 32) >> 4), "n"(((6 >> 2) * (128 * 128) + (6 & 3) * 32) >> 4), "n"(((7 >> 2) * (128 * 128) + (7 & 3) * 32) >> 4)
+      : "memory");
+}
+// O += P V for 64 key rows: 4 k-steps, A = P from TMEM (8 columns per step), B = V MN-major (2 KB per step).
+__device__ __forceinline__ void pv_block4(uint32_t d_tmem, uint32_t p_tmem, uint32_t v_lo, uint32_t hi, uint32_t idesc,
+                                          uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred pt, pa;\n\t.reg .b32 ta, tb;\n\t.reg .b64 db;\n\t"
+      "setp.eq.u32 pt, %3, %3;\n\tsetp.ne.b32 pa, %5, 0;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, pa;\n\t"
+      "add.u32 ta, %1, 8;\n\tadd.u32 tb, %2, 128;\n\tmov.b64 db, {tb, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %4, pt;\n\t"
+      "add.u32 ta, %1, 16;\n\tadd.u32 tb, %2, 256;\n\tmov.b64 db, {tb, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %4, pt;\n\t"
+      "add.u32 ta, %1, 24;\n\tadd.u32 tb, %2, 384;\n\tmov.b64 db, {tb, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %4, pt;\n\t"
+      "}"
+      ::"r"(d_tmem), "r"(p_tmem), "r"(v_lo), "r"(hi), "r"(idesc), "r"(acc)
+      : "memory");
 }
 #define XDIT_R32(a, o) \
   "=r"(a[o + 0]), "=r"(a[o + 1]), "=r"(a[o + 2]), "=r"(a[o + 3]), "=r"(a[o + 4]), "=r"(a[o + 5]), "=r"(a[o + 6]), \
@@ -449,84 +503,115 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_sm100_kernel(const __gri
     }
     } else if (warp == 8) {
     // ======================= MMA issuer =======================
-    if (lane == 0) {
+    // The whole warp runs this role converged and one elected lane issues the tcgen05 instructions:
+    // descriptors, TMEM addresses and barrier addresses are then warp-uniform values which the
+    // compiler can keep in uniform registers, where tcgen05.mma / tcgen05.commit take their operands.
+    // (Inside a single-lane branch every operand is first moved over from a vector register, and
+    // that traffic, not the tensor pipe, set the pace of S = Q K^T.)
+    {
+      const bool leader = elect_one();
+      const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
       const uint32_t idesc_qk = make_idesc(BF16, false, kTile);
       const uint32_t idesc_pv = make_idesc(BF16, true, a.dv_n);
       const int dk16 = a.dk16;
-      const int last_t = tile_on[1] ? 1 : 0;
+      const bool two = tile_on[1];  // tile 0 exists in every launched CTA
       bool ok = true;
+      const uint32_t kdesc_hi = (uint32_t)(desc_kmajor(0) >> 32), vdesc_hi = (uint32_t)(desc_mnmajor(0) >> 32);
+      const uint32_t q_lo = (uint32_t)desc_kmajor(q_smem);
+      const uint32_t kv_lo = (uint32_t)desc_kmajor(kv_smem);
+      // the low words of the K-major and MN-major forms differ in the leading-offset field only
+      constexpr uint32_t v_lo_delta = (uint32_t)((kSlabBytes >> 4) - 1) << 16;
+      auto wait_all = [&](uint32_t bar, uint32_t parity, int code) {
+        return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, code));
+      };
+      // S_t = Q_t K^T (call from the elected lane only)
       auto issue_qk = [&](int t, int stage) {
-        const uint32_t qa = q_smem + t * L::kQTileBytes;
-        const uint32_t kb = kv_smem + stage * L::kStageBytes;
-        for (int ks = 0; ks < dk16; ++ks) {
-          const uint32_t off = (ks >> 2) * kSlabBytes + (ks & 3) * 32;
-          tc_mma_ss(tmem_base + t * kTile, desc_kmajor(qa + off), desc_kmajor(kb + off), idesc_qk, ks > 0);
+        const uint32_t qa = q_lo + (uint32_t)(t * (L::kQTileBytes >> 4));
+        const uint32_t kb = kv_lo + (uint32_t)(stage * (L::kStageBytes >> 4));
+        const uint32_t d = tmem_u + t * kTile;
+        if (dk16 == 8) {
+          qk_block8(d, qa, kb, kdesc_hi, idesc_qk);
+        } else {
+          for (int ks = 0; ks < dk16; ++ks) {
+            const uint32_t off = ((ks >> 2) * kSlabBytes + (ks & 3) * 32) >> 4;
+            tc_mma_ss(d, ((uint64_t)kdesc_hi << 32) | (qa + off), ((uint64_t)kdesc_hi << 32) | (kb + off), idesc_qk,
+                      ks > 0);
+          }
         }
       };
       // O_t += P_t[:, 64*half : 64*half+64] V[64*half : 64*half+64, :]   (4 steps of 16 key rows)
       auto issue_pv_half = [&](int t, int stage, int half, bool first_tile) {
-        const uint32_t vb = kv_smem + stage * L::kStageBytes;
-        for (int ks = 4 * half; ks < 4 * half + 4; ++ks)
-          tc_mma_ts(tmem_base + 256 + t * kTile, tmem_base + t * kTile + ks * 8, desc_mnmajor(vb + ks * 2048),
-                    idesc_pv, (!first_tile) || ks > 0);
+        const uint32_t vb = kv_lo + v_lo_delta + (uint32_t)(stage * (L::kStageBytes >> 4)) + half * (4 * 2048 >> 4);
+        pv_block4(tmem_u + 256 + t * kTile, tmem_u + t * kTile + half * 32, vb, vdesc_hi, idesc_pv,
+                  (first_tile && half == 0) ? 0u : 1u);
       };
       // prologue: S_t(0) = Q_t K(0)^T
-      ok = mbar_wait(bar_kv_full(0), 0, abort_flag, 200);
+      ok = wait_all(bar_kv_full(0), 0, 200);
       for (int t = 0; t < 2 && ok; ++t) {
-        if (!tile_on[t]) continue;
-        ok = mbar_wait(bar_q_full(t), 0, abort_flag, 201 + t);
+        if (t == 1 && !two) continue;
+        ok = wait_all(bar_q_full(t), 0, 201 + t);
         if (!ok) break;
         tc_fence_after();
-        issue_qk(t, 0);
-        tc_commit(bar_s_full(t));
+        if (leader) {
+          issue_qk(t, 0);
+          tc_commit(bar_s_full(t));
+        }
       }
-      if (ok) tc_commit(bar_kv_empty(0));
+      if (ok && leader) tc_commit(bar_kv_empty(0));
+      // ring cursors: V(j) is item 2j+1, K(j+1) item 2j+2
+      int sv = 1 % NSTAGE, pv = 0, sk = 2 % NSTAGE, pk = 0;
+      auto advance2 = [&](int& st, int& ph) {
+        st += 2;
+        if (st >= NSTAGE) { st -= NSTAGE; ph ^= 1; }
+      };
       for (int j = 0; j < n_tiles && ok; ++j) {
-        const int iv = 2 * j + 1, sv = iv % NSTAGE;
-        const int ik = 2 * j + 2, sk = ik % NSTAGE;
         const bool more = j + 1 < n_tiles;
-        ok = mbar_wait(bar_kv_full(sv), (iv / NSTAGE) & 1, abort_flag, 210);
+        ok = wait_all(bar_kv_full(sv), pv, 210);
         for (int t = 0; t < 2 && ok; ++t) {
-          if (!tile_on[t]) continue;
+          if (t == 1 && !two) continue;
+          const bool last_tile = two ? t == 1 : true;
           // P arrives in two halves (64 key columns each): the first half of O += P V runs while
           // the softmax group still computes the second half
-          ok = mbar_wait(bar_p_full(t, 0), j & 1, abort_flag, 220 + t);
+          ok = wait_all(bar_p_full(t, 0), j & 1, 220 + t);
           if (!ok) break;
           tc_fence_after();
           if (t == 0) XDIT_TRACE(2, j, 0);
-          issue_pv_half(t, sv, 0, j == 0);
+          if (leader) issue_pv_half(t, sv, 0, j == 0);
           if (t == 0) XDIT_TRACE(2, j, 1);
-          ok = mbar_wait(bar_p_full(t, 1), j & 1, abort_flag, 222 + t);
+          if (more && t == 0) {
+            // K(j+1) has long arrived; taking the wait here keeps it out of the single-lane region below
+            ok = wait_all(bar_kv_full(sk), pk, 230);
+            if (!ok) break;
+          }
+          ok = wait_all(bar_p_full(t, 1), j & 1, 222 + t);
           if (!ok) break;
           tc_fence_after();
           if (t == 0) XDIT_TRACE(2, j, 2);
-          issue_pv_half(t, sv, 1, j == 0);
-          if (t == 0) XDIT_TRACE(2, j, 3);
-          if (t == last_t) tc_commit(bar_kv_empty(sv));  // V(j) is free once both tiles' PV retire
-          if (more) {
-            if (t == 0 || !tile_on[0]) {
-              ok = mbar_wait(bar_kv_full(sk), (ik / NSTAGE) & 1, abort_flag, 230);
-              if (!ok) break;
-              tc_fence_after();
+          if (leader) {
+            issue_pv_half(t, sv, 1, j == 0);
+            if (last_tile) tc_commit(bar_kv_empty(sv));  // V(j) is free once both tiles' PV retire
+            if (more) {
+              issue_qk(t, sk);
+              // completes after every MMA issued so far, i.e. it also tells the softmax group that
+              // O_t holds the sum up to key tile j
+              tc_commit(bar_s_full(t));
+              if (last_tile) tc_commit(bar_kv_empty(sk));
+            } else {
+              tc_commit(bar_o_full(t));
             }
-            if (t == 0) XDIT_TRACE(2, j, 4);
-            issue_qk(t, sk);
-            if (t == 0) XDIT_TRACE(2, j, 5);
-            // completes after every MMA issued so far, i.e. it also tells the softmax group that
-            // O_t holds the sum up to key tile j
-            tc_commit(bar_s_full(t));
-            if (t == 0) XDIT_TRACE(2, j, 6);
-          } else {
-            tc_commit(bar_o_full(t));
           }
+          if (t == 0) XDIT_TRACE(2, j, 6);
         }
         if (!ok) break;
-        if (more) tc_commit(bar_kv_empty(sk));
+        advance2(sv, pv);
+        advance2(sk, pk);
       }
       if (!ok) {
         // drain the tensor pipe before TMEM is released
-        tc_commit(bar_drain);
-        for (int it = 0; it < (1 << 20) && !mbar_try_wait(bar_drain, 0); ++it) __nanosleep(64);
+        if (leader) tc_commit(bar_drain);
+        if (lane == 0)
+          for (int it = 0; it < (1 << 20) && !mbar_try_wait(bar_drain, 0); ++it) __nanosleep(64);
+        __syncwarp();
       }
     }
     }
