@@ -76,7 +76,7 @@ def test_combined_equals_separate(ops, monkeypatch):
     from xdit_b200 import usp
 
     monkeypatch.setattr(usp, "get_ulysses_parallel_world_size", lambda: 2)
-    monkeypatch.setattr(usp, "_sdpa_all_to_all_single", lambda t: t)
+    monkeypatch.setattr(usp, "_sdpa_all_to_all_single", lambda t, group=None: t)
     q, k, v = (rand((2, 4, 128, 64), torch.bfloat16, i) for i in range(3))
     cq, ck, cv = usp._combined_qkv_all_to_all(q, k, v)
     for a, b in zip((cq, ck, cv), (q, k, v)):
