@@ -157,20 +157,24 @@ def run_reference(args, w, name):
     S, D = w["S"], w["D"]
     g = torch.Generator().manual_seed(0)
 
-    def one(heads):
-        q, k, v = (torch.randn(1, heads, S, D, generator=g) for _ in range(3))
+    def make(heads):
+        return tuple(torch.randn(1, heads, S, D, generator=g) for _ in range(3))
+
+    def one(qkv):
         t0 = time.perf_counter()
-        O.attention_dense_torch_cpu(q, k, v)
+        O.attention_dense_torch_cpu(*qkv)
         return time.perf_counter() - t0
 
-    t_head = one(1)
-    budget = 150.0 / max(1, args.steps + args.warmup)
+    # size the per-step sample (a number of heads of one layer) so that the whole run stays near 90 s
+    t_head = one(make(1))
+    budget = 90.0 / max(1, args.steps + args.warmup)
     heads = int(max(1, min(w["H"], budget / max(t_head, 1e-3))))
+    qkv = make(heads)  # one input set, larger than any CPU cache (heads x 75,600 x 128 fp32 x 3)
     for _ in range(args.warmup):
-        one(heads)
+        one(qkv)
     total = 0.0
     for _ in range(args.steps):
-        total += one(heads)
+        total += one(qkv)
     fl = 4.0 * S * S * heads * D
     val = fl * args.steps / total / 1e12
     sample = (f"{heads} of {w['H']} heads of one layer, {S} tokens, fp32 torch CPU SDPA "

@@ -197,6 +197,34 @@ XDIT_API int xdit_merge_out_lse(float* o_acc, float* lse_acc, const void* out_b,
                        void* out_final, int32_t dtype, int64_t rows, int32_t D, int32_t first,
                        void* stream);
 
+/* Attention prologue of the DiT processors fused with the Ulysses pack, for the projections of one
+ * layer: q and k are RMS-normalised (over all H*D elements of a token when norm_per_head == 0, over
+ * each head's D elements otherwise; a NULL weight skips the norm of that tensor), rotated
+ * (interleaved pairs (2i, 2i+1): out[2i] = x1*cos[2i] - x2*sin[2i+1], out[2i+1] = x1*sin[2i+1] +
+ * x2*cos[2i]; NULL cos skips it), split into heads and written, together with v, in the all-to-all
+ * send layout [U][H/U][B][s][D] (peer blocks dst_*_peer_stride elements apart; U = 1 gives
+ * [H][B][s][D]).  q, k, v: [B, s, H*D] with element strides, innermost contiguous; weights [H*D]
+ * (or [D] with norm_per_head) in `dtype`; cos, sin: fp32 [s, D] rows cos_sin_stride_row apart.
+ * dtype bf16 or fp16; D % 8 == 0; H*D <= 8192; with norm_per_head D/8 must be a power of two <= 32.
+ * Replaces: norm_q / norm_k, the inline apply_rotary_emb, unflatten + transpose
+ * (xfuser/model_executor/models/transformers/transformer_wan.py:97-122, 143-147; the same steps at
+ * transformer_flux.py:113-147, 170-172) and the re-layout copies of _ft_c_input_all_to_all
+ * (xfuser/model_executor/layers/usp.py:96-108). */
+struct xdit_prologue_params {
+  int32_t dtype;
+  int32_t B, H, D, s, U;
+  int32_t norm_per_head;
+  float eps;
+  const void *q, *k, *v;
+  int64_t q_stride_b, q_stride_row, k_stride_b, k_stride_row, v_stride_b, v_stride_row;
+  const void *norm_q_weight, *norm_k_weight;
+  const float *cos, *sin;
+  int64_t cos_sin_stride_row;
+  void *dst_q, *dst_k, *dst_v;
+  int64_t dst_q_peer_stride, dst_k_peer_stride, dst_v_peer_stride;
+};
+XDIT_API int xdit_qk_norm_rope_pack(const struct xdit_prologue_params* p, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

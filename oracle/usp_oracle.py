@@ -36,6 +36,9 @@ __all__ = [
     "KVCacheOracle",
     "long_context_attention_bshd",
     "ring_flash_attn_bshd",
+    "rms_norm",
+    "rope_interleaved",
+    "attention_prologue",
 ]
 
 
@@ -434,3 +437,59 @@ def long_context_attention_bshd(q_shards, k_shards, v_shards, U, R, joint_query=
         for j, g in enumerate(grp):
             out[g] = oo[j]
     return out
+
+
+# --------------------------------------------------------------------------------------
+# attention prologue of the DiT processors (norm, rotary embedding, head split, pack)
+# --------------------------------------------------------------------------------------
+def rms_norm(x, weight, eps, group=None):
+    """``torch.nn.RMSNorm`` over the last axis as the processors apply it to the q and k projections:
+    ``attn.norm_q(query)`` on ``[B, s, H*D]`` in ``transformer_wan.py:99-100`` (``group=None``: one mean
+    of squares over all ``H*D`` elements) or on ``[B, s, H, D]`` in ``transformer_flux.py:121-122``
+    (``group=D``: one per head).  ``weight`` has ``group`` (or ``H*D``) elements."""
+    x = np.asarray(x, dtype=np.float64)
+    shape = x.shape
+    g = shape[-1] if group is None else group
+    xg = x.reshape(shape[:-1] + (shape[-1] // g, g))
+    y = xg / np.sqrt(np.mean(xg * xg, axis=-1, keepdims=True) + eps)
+    y = y.reshape(shape)
+    w = np.asarray(weight, dtype=np.float64)
+    if w.size == shape[-1]:
+        return y * w
+    return (y.reshape(shape[:-1] + (shape[-1] // g, g)) * w).reshape(shape)
+
+
+def rope_interleaved(x, cos, sin):
+    """Rotary embedding of interleaved pairs, ``transformer_wan.py:108-120``: with
+    ``x1, x2 = x[..., 0::2], x[..., 1::2]``, ``out[..., 0::2] = x1*cos[..., 0::2] - x2*sin[..., 1::2]`` and
+    ``out[..., 1::2] = x1*sin[..., 1::2] + x2*cos[..., 0::2]``.  ``x`` is ``[B, s, H, D]``, ``cos`` / ``sin``
+    broadcast against it (``[1, s, 1, D]``)."""
+    x = np.asarray(x, dtype=np.float64)
+    cos = np.asarray(cos, dtype=np.float64)[..., 0::2]
+    sin = np.asarray(sin, dtype=np.float64)[..., 1::2]
+    x1, x2 = x[..., 0::2], x[..., 1::2]
+    out = np.empty_like(x)
+    out[..., 0::2] = x1 * cos - x2 * sin
+    out[..., 1::2] = x1 * sin + x2 * cos
+    return out
+
+
+def attention_prologue(q, k, v, heads, wq=None, wk=None, eps=1e-6, per_head=False, cos=None, sin=None, U=1):
+    """What a DiT attention processor does between the q/k/v projections and the attention call
+    (``transformer_wan.py:97-122,143-147``), followed by the send layout of the Ulysses all-to-all
+    (``usp.py:96-108``): norm of q and k, unflatten to heads, rotary embedding of q and k, and for each
+    tensor the re-layout ``[B, s, H, D] -> [U][H/U][B][s][D]``.  ``q, k, v`` are ``[B, s, H*D]``;
+    ``cos`` / ``sin`` are ``[s, D]``.  Returns the three send buffers as arrays of that 5-D shape."""
+    outs = []
+    for i, (x, w) in enumerate(((q, wq), (k, wk), (v, None))):
+        x = np.asarray(x, dtype=np.float64)
+        B, s, HD = x.shape
+        D = HD // heads
+        if w is not None:
+            x = rms_norm(x, w, eps, group=D if per_head else None)
+        x = x.reshape(B, s, heads, D)
+        if cos is not None and i < 2:  # q and k only
+            x = rope_interleaved(x, np.asarray(cos)[None, :, None, :], np.asarray(sin)[None, :, None, :])
+        # [B, s, H, D] -> [U, H/U, B, s, D]
+        outs.append(x.transpose(2, 0, 1, 3).reshape(U, heads // U, B, s, D))
+    return tuple(outs)

@@ -89,12 +89,23 @@ def merge_out_lse(o_acc, lse_acc, out_b, lse_b, first, out_final=None):
         out_final.copy_(o_acc.to(out_final.dtype))
 
 
+def qk_norm_rope_pack(q, k, v, heads, dst_q, dst_k, dst_v, peer_strides, U=1, *, norm_q_weight=None,
+                      norm_k_weight=None, eps=1e-6, norm_per_head=False, cos=None, sin=None):
+    n = lambda t: None if t is None else _np(t)
+    outs = O.attention_prologue(_np(q), _np(k), _np(v), heads, n(norm_q_weight), n(norm_k_weight), eps,
+                                norm_per_head, n(cos), n(sin), U)
+    for o, dst, stride in zip(outs, (dst_q, dst_k, dst_v), peer_strides):
+        blk = o[0].size
+        for p in range(U):
+            dst[p * stride:p * stride + blk].copy_(torch.from_numpy(o[p].reshape(-1)).to(dst.dtype))
+
+
 def install(monkeypatch_or_none=None):
     """Replace the CUDA wrappers of ``xdit_b200.ops`` with the CPU stand-ins above."""
     import xdit_b200.ops as ops
 
     names = ["attn_fwd", "ulysses_pack", "ulysses_unpack_in", "ulysses_pack_out", "ulysses_unpack_out",
-             "kv_patch_update", "merge_out_lse"]
+             "kv_patch_update", "merge_out_lse", "qk_norm_rope_pack"]
     for n in names:
         if monkeypatch_or_none is not None:
             monkeypatch_or_none.setattr(ops, n, globals()[n])

@@ -364,8 +364,64 @@ def _usp_kvcache_worker(rank, world, port, outdir):
     dist.destroy_process_group()
 
 
+def _reference_wan_rope():
+    """The rotary-embedding function the reference defines inline in its Wan attention processor
+    (``xfuser/model_executor/models/transformers/transformer_wan.py:108-120``), taken from the file's
+    syntax tree at generation time and executed as it is (importing the module would need diffusers)."""
+    import ast
+
+    path = os.path.join(REF, "xfuser", "model_executor", "models", "transformers", "transformer_wan.py")
+    src = open(path).read()
+    for node in ast.walk(ast.parse(src)):
+        if isinstance(node, ast.FunctionDef) and node.name == "apply_rotary_emb":
+            ns = {"torch": torch}
+            exec(ast.get_source_segment(src, node), ns)
+            return ns["apply_rotary_emb"]
+    raise RuntimeError("apply_rotary_emb not found in the reference's Wan processor")
+
+
+def _prologue_cases(outdir):
+    """q/k/v projections -> what the processor hands to USP (``transformer_wan.py:97-122,143-147``):
+    norm_q / norm_k (``torch.nn.RMSNorm``; the module objects are built by diffusers, which is absent,
+    so they are constructed here with the same arguments: full hidden size, ``elementwise_affine``),
+    unflatten to heads, the reference's own rotary function, transpose to [B, H, s, D].  The second case
+    applies the norm per head, as the Flux processor does (``transformer_flux.py:117-122``)."""
+    rope = _reference_wan_rope()
+    g = torch.Generator().manual_seed(77)
+    B, s, H, D = 2, 24, 4, 16
+    eps = 1e-6
+    q, k, v = (torch.randn(B, s, H * D, generator=g) for _ in range(3))
+    pos = torch.arange(s, dtype=torch.float32)[:, None]
+    inv = 1.0 / (10000.0 ** (torch.arange(0, D, 2, dtype=torch.float32) / D))
+    ang = (pos * inv[None, :]).repeat_interleave(2, dim=1)  # [s, D], each frequency twice
+    # distinct even/odd entries as well, so that which column the reference reads is pinned
+    cos = torch.cos(ang) + 0.01 * torch.randn(s, D, generator=g)
+    sin = torch.sin(ang) + 0.01 * torch.randn(s, D, generator=g)
+    fc, fs = cos[None, :, None, :], sin[None, :, None, :]
+    for name, per_head in (("prologue_wan.npz", False), ("prologue_per_head.npz", True)):
+        nq = torch.nn.RMSNorm(D if per_head else H * D, eps=eps, elementwise_affine=True)
+        nk = torch.nn.RMSNorm(D if per_head else H * D, eps=eps, elementwise_affine=True)
+        with torch.no_grad():
+            nq.weight.copy_(1.0 + 0.1 * torch.randn(nq.weight.shape, generator=g))
+            nk.weight.copy_(1.0 + 0.1 * torch.randn(nk.weight.shape, generator=g))
+            if per_head:
+                qq, kk = nq(q.unflatten(2, (H, -1))), nk(k.unflatten(2, (H, -1)))
+            else:
+                qq, kk = nq(q).unflatten(2, (H, -1)), nk(k).unflatten(2, (H, -1))
+            vv = v.unflatten(2, (H, -1))
+            qq, kk = rope(qq, fc, fs), rope(kk, fc, fs)
+            outs = [t.transpose(1, 2).contiguous().numpy() for t in (qq, kk, vv)]
+        np.savez_compressed(os.path.join(outdir, name), q=q.numpy(), k=k.numpy(), v=v.numpy(), cos=cos.numpy(),
+                            sin=sin.numpy(), wq=nq.weight.detach().numpy(), wk=nk.weight.detach().numpy(),
+                            eps=np.array(eps), heads=np.array(H), per_head=np.array(int(per_head)),
+                            q_out=outs[0], k_out=outs[1], v_out=outs[2])
+
+
 def main():
     outdir = HERE
+    if "--prologue-only" in sys.argv:
+        _prologue_cases(outdir)
+        return
     port = 29611
     for world in (1, 2, 4):
         cases = [c for c in USP_CASES if c[1] * c[2] == world]
@@ -376,6 +432,7 @@ def main():
     mp.spawn(_usp_kvcache_worker, args=(2, port, outdir), nprocs=2, join=True)
     _layout_cases(outdir)
     _cache_cases(outdir)
+    _prologue_cases(outdir)
     print("golden fixtures written to", outdir)
 
 

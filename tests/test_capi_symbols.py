@@ -46,8 +46,9 @@ def test_struct_sizes_match_header():
 #include <stdio.h>
 #include "xdit_b200.h"
 int main(void) {
-  printf("%zu %zu %zu %zu %zu\n", sizeof(struct xdit_caps), sizeof(struct xdit_seq),
-         sizeof(struct xdit_attn_params), sizeof(struct xdit_pack_job), sizeof(struct xdit_kv_patch_params));
+  printf("%zu %zu %zu %zu %zu %zu\n", sizeof(struct xdit_caps), sizeof(struct xdit_seq),
+         sizeof(struct xdit_attn_params), sizeof(struct xdit_pack_job), sizeof(struct xdit_kv_patch_params),
+         sizeof(struct xdit_prologue_params));
   return 0;
 }'''
     with tempfile.TemporaryDirectory() as d:
@@ -56,7 +57,7 @@ int main(void) {
         exe = os.path.join(d, "probe")
         subprocess.run(["gcc", "-I", os.path.join(ROOT, "include"), c, "-o", exe], check=True)
         sizes = [int(x) for x in subprocess.run([exe], capture_output=True, text=True, check=True).stdout.split()]
-    mirrors = [_capi.Caps, _capi.Seq, _capi.AttnParams, _capi.PackJob, _capi.KvPatchParams]
+    mirrors = [_capi.Caps, _capi.Seq, _capi.AttnParams, _capi.PackJob, _capi.KvPatchParams, _capi.PrologueParams]
     assert sizes == [ctypes.sizeof(m) for m in mirrors]
 
 

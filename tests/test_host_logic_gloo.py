@@ -7,7 +7,7 @@ import pytest
 
 import os
 
-from tests.usp_worker import HERE, golden_files, run, run_kv
+from tests.usp_worker import HERE, golden_files, run, run_kv, run_prologue
 
 
 @pytest.mark.parametrize("mode", ["usp", "legacy", "compat", "yunchang"])
@@ -56,3 +56,10 @@ def test_stale_kv_under_ulysses_matches_reference():
     """USP(attn_layer=...) with PipeFusion patches and Ulysses degree 2: the fresh rows reach the cache
     manager as two segments of the all-to-all receive buffer."""
     run_kv(2, os.path.join(HERE, "golden", "uspkv_u2r1.npz"), 29741)
+
+
+@pytest.mark.parametrize("U,R", [(2, 1), (1, 2)])
+def test_attention_from_projections_two_ranks(U, R):
+    """The processor slice (norm, rotary embedding, head split, USP, head merge) against the oracle:
+    Ulysses 2 takes the fused send-buffer path, ring 2 the [B,H,s,D] hand-over to USP."""
+    run_prologue(2, U, R, 29745 + R)

@@ -194,3 +194,20 @@ def test_usp_with_stale_kv_under_ulysses(golden_dir):
     for r in range(U):
         np.testing.assert_allclose(out0[r], z["out0"][r], atol=2e-5, rtol=1e-4)
         np.testing.assert_allclose(out1[r], z["out1"][r], atol=2e-5, rtol=1e-4)
+
+
+@pytest.mark.parametrize("name", ["prologue_wan.npz", "prologue_per_head.npz"])
+def test_attention_prologue_matches_reference(name):
+    """Norm + rotary embedding + head split against the reference's own code path
+    (torch.nn.RMSNorm and the rotary function of transformer_wan.py:108-120, see make_golden.py)."""
+    z = np.load(os.path.join(HERE, "golden", name))
+    H, per_head = int(z["heads"]), bool(z["per_head"])
+    outs = O.attention_prologue(z["q"], z["k"], z["v"], H, z["wq"], z["wk"], float(z["eps"]), per_head,
+                                z["cos"], z["sin"], U=1)
+    for got, key in zip(outs, ("q_out", "k_out", "v_out")):
+        assert np.abs(got[0].transpose(1, 0, 2, 3) - z[key]).max() < 2e-6, key
+    # send layout for two peers: peer p holds heads [p*H/2, (p+1)*H/2)
+    q2 = O.attention_prologue(z["q"], z["k"], z["v"], H, z["wq"], z["wk"], float(z["eps"]), per_head,
+                              z["cos"], z["sin"], U=2)[0]
+    for p in range(2):
+        assert np.abs(q2[p].transpose(1, 0, 2, 3) - z["q_out"][:, p * H // 2:(p + 1) * H // 2]).max() < 2e-6

@@ -135,6 +135,87 @@ def _yunchang_shaped_forward(xdit_b200, ql, kl, vl, kw, strat, rank, U, R, dev):
     return out
 
 
+def prologue_worker(rank, world, port, U, R, errq, backend="gloo", dtype_name="float32", tol=5e-5):
+    """attention_from_projections under U x R ranks against the oracle: prologue on the global
+    projections, dense attention, rows of this rank."""
+    try:
+        sys.path.insert(0, ROOT)
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        gpu = backend == "nccl"
+        if gpu:
+            torch.cuda.set_device(rank)
+            dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        else:
+            dist.init_process_group("gloo", rank=rank, world_size=world)
+            torch.set_num_threads(1)
+        import xdit_b200
+        from oracle import usp_oracle as O
+        from xdit_b200.prologue import attention_from_projections
+
+        if not gpu:
+            from tests import fake_ops
+
+            fake_ops.install()
+        dtype = getattr(torch, dtype_name)
+        dev = torch.device("cuda", rank) if gpu else torch.device("cpu")
+        xdit_b200.init_sequence_parallel(U, R, backend=backend)
+        B, S, H, D = 1, 64 * world, 4, 32
+        g = torch.Generator().manual_seed(5)
+        q, k, v = (torch.randn(B, S, H * D, generator=g).to(dtype) for _ in range(3))
+        wq, wk = (1 + 0.1 * torch.randn(H * D, generator=g)).to(dtype), (1 + 0.1 * torch.randn(H * D, generator=g)).to(dtype)
+        ang = torch.rand(S, D // 2, generator=g) * 6.28
+        cos, sin = torch.cos(ang).repeat_interleave(2, 1), torch.sin(ang).repeat_interleave(2, 1)
+        for per_head in (False, True):
+            w_q, w_k = (wq[:D].contiguous(), wk[:D].contiguous()) if per_head else (wq, wk)
+            n64 = lambda t: t.double().numpy()
+            qs, ks, vs = O.attention_prologue(n64(q), n64(k), n64(v), H, n64(w_q), n64(w_k), 1e-6, per_head,
+                                              n64(cos), n64(sin), 1)
+            want, _ = O.attention_dense(*(x[0].transpose(1, 0, 2, 3) for x in (qs, ks, vs)))  # [B,H,S,D]
+            want = want.transpose(0, 2, 1, 3).reshape(B, S, H * D)
+            sl = slice(rank * (S // world), (rank + 1) * (S // world))
+            put = lambda t: t.to(dev)
+            got = attention_from_projections(
+                put(q[:, sl]), put(k[:, sl]), put(v[:, sl]), H, norm_q_weight=put(w_q), norm_k_weight=put(w_k),
+                eps=1e-6, norm_per_head=per_head, rotary_emb=(put(cos[sl])[None, :, None, :], put(sin[sl])[None, :, None, :]))
+            if gpu:
+                torch.cuda.synchronize()
+                from xdit_b200 import ops
+
+                ops.check_status()
+            assert tuple(got.shape) == (B, S // world, H * D)
+            err = (got.double().cpu() - torch.from_numpy(want[:, sl])).abs().max().item()
+            assert err < tol, ("prologue", U, R, per_head, rank, err)
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception as e:
+        import traceback
+
+        errq.put(f"rank {rank}: {e}\n{traceback.format_exc()}")
+        raise
+
+
+def run_prologue(world, U, R, port, **kw):
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    errq = ctx.SimpleQueue()
+    procs = [ctx.Process(target=prologue_worker, args=(r, world, port, U, R, errq), kwargs=kw) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+    errs = []
+    while not errq.empty():
+        errs.append(errq.get())
+    for p in procs:
+        if p.is_alive():
+            p.terminate()
+            errs.append("a rank did not finish")
+    assert not errs and all(p.exitcode == 0 for p in procs), "\n".join(errs)
+
+
 def kv_worker(rank, world, port, path, errq, backend="gloo", dtype_name="float32", tol=5e-5):
     """USP with the PipeFusion stale-KV buffer under Ulysses: warm-up step, then a patch step."""
     try:

@@ -28,6 +28,7 @@ EXPORTS = [
     "xdit_ulysses_unpack_in",
     "xdit_kv_patch_update",
     "xdit_merge_out_lse",
+    "xdit_qk_norm_rope_pack",
 ]
 
 
@@ -82,6 +83,20 @@ class KvPatchParams(C.Structure):
     ]
 
 
+class PrologueParams(C.Structure):
+    _fields_ = [
+        ("dtype", C.c_int32), ("B", C.c_int32), ("H", C.c_int32), ("D", C.c_int32), ("s", C.c_int32),
+        ("U", C.c_int32), ("norm_per_head", C.c_int32), ("eps", C.c_float),
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p),
+        ("q_stride_b", C.c_int64), ("q_stride_row", C.c_int64), ("k_stride_b", C.c_int64),
+        ("k_stride_row", C.c_int64), ("v_stride_b", C.c_int64), ("v_stride_row", C.c_int64),
+        ("norm_q_weight", C.c_void_p), ("norm_k_weight", C.c_void_p),
+        ("cos", C.c_void_p), ("sin", C.c_void_p), ("cos_sin_stride_row", C.c_int64),
+        ("dst_q", C.c_void_p), ("dst_k", C.c_void_p), ("dst_v", C.c_void_p),
+        ("dst_q_peer_stride", C.c_int64), ("dst_k_peer_stride", C.c_int64), ("dst_v_peer_stride", C.c_int64),
+    ]
+
+
 _lib = None
 
 
@@ -119,6 +134,8 @@ def load() -> C.CDLL:
         fn.restype = C.c_int
     lib.xdit_kv_patch_update.argtypes = [C.POINTER(KvPatchParams), C.c_void_p]
     lib.xdit_kv_patch_update.restype = C.c_int
+    lib.xdit_qk_norm_rope_pack.argtypes = [C.POINTER(PrologueParams), C.c_void_p]
+    lib.xdit_qk_norm_rope_pack.restype = C.c_int
     lib.xdit_merge_out_lse.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                        C.c_int32, C.c_int64, C.c_int32, C.c_int32, C.c_void_p]
     lib.xdit_merge_out_lse.restype = C.c_int

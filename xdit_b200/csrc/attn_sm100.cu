@@ -4,7 +4,8 @@
 // One CTA owns two query tiles of 128 rows and walks all key/value tiles of 128 rows.
 //   warps 0-3  softmax group for query tile 0   (one thread per query row)
 //   warps 4-7  softmax group for query tile 1
-//   warp  8    issues every tcgen05.mma (one lane) and owns the TMEM allocation
+//   warp  8    issues every tcgen05.mma (the warp runs converged, one elected lane issues) and owns
+//               the TMEM allocation
 //   warp  9    issues every TMA load (one lane)
 //   warps 10-11 idle: they complete the warpgroup that hands its registers to the softmax warps
 //               (setmaxnreg: 40 registers for warps 8-11, 232 for warps 0-7)

@@ -130,6 +130,39 @@ int xdit_ulysses_pack(const struct xdit_pack_job* jobs, int32_t njobs, int32_t d
   return launch_row_copy(rc, n, (cudaStream_t)stream);
 }
 
+int xdit_qk_norm_rope_pack(const struct xdit_prologue_params* p, void* stream) {
+  if (!p) { set_error("xdit_qk_norm_rope_pack: NULL params"); return XDIT_E_NULL; }
+  if (p->dtype != XDIT_BF16 && p->dtype != XDIT_F16) {
+    set_error("xdit_qk_norm_rope_pack: dtype %d (bf16 or fp16)", p->dtype);
+    return XDIT_E_DTYPE;
+  }
+  if (p->B < 1 || p->H < 1 || p->D < 8 || p->s < 1 || p->U < 1 || p->H % p->U || p->D % 8 ||
+      (int64_t)p->H * p->D > 8192) {
+    set_error("xdit_qk_norm_rope_pack: B=%d H=%d D=%d s=%d U=%d (D %% 8 == 0, H %% U == 0, H*D <= 8192)", p->B, p->H,
+              p->D, p->s, p->U);
+    return XDIT_E_SHAPE;
+  }
+  const int vpd = p->D / 8;
+  if (p->norm_per_head && (p->norm_q_weight || p->norm_k_weight) && (vpd > 32 || (vpd & (vpd - 1)))) {
+    set_error("xdit_qk_norm_rope_pack: per-head norm needs D/8 to be a power of two up to 32 (D=%d)", p->D);
+    return XDIT_E_SHAPE;
+  }
+  if (!p->q || !p->k || !p->v || !p->dst_q || !p->dst_k || !p->dst_v || ((p->cos == nullptr) != (p->sin == nullptr))) {
+    set_error("xdit_qk_norm_rope_pack: NULL pointer (cos and sin go together)");
+    return XDIT_E_NULL;
+  }
+  const uintptr_t ptrs = (uintptr_t)p->q | (uintptr_t)p->k | (uintptr_t)p->v | (uintptr_t)p->dst_q |
+                         (uintptr_t)p->dst_k | (uintptr_t)p->dst_v | (uintptr_t)p->norm_q_weight |
+                         (uintptr_t)p->norm_k_weight | (uintptr_t)p->cos | (uintptr_t)p->sin;
+  const int64_t strides = p->q_stride_b | p->q_stride_row | p->k_stride_b | p->k_stride_row | p->v_stride_b |
+                          p->v_stride_row | p->dst_q_peer_stride | p->dst_k_peer_stride | p->dst_v_peer_stride;
+  if ((ptrs & 15) || (strides & 7) || (p->cos && (p->cos_sin_stride_row & 3))) {
+    set_error("xdit_qk_norm_rope_pack: pointers must be 16-byte aligned and strides multiples of 8 elements");
+    return XDIT_E_ALIGN;
+  }
+  return launch_prologue(*p, (cudaStream_t)stream);
+}
+
 int xdit_ulysses_pack_out(const void* src, int64_t stride_b, int64_t stride_h, int64_t stride_row,
                           void* dst, int32_t dtype, int32_t B, int32_t Hl, int32_t S, int32_t D,
                           void* stream) {

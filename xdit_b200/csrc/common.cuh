@@ -50,4 +50,7 @@ int launch_attn_generic(const xdit_attn_params& p, cudaStream_t stream);
 int attn_sm100_applicable(const xdit_attn_params& p);
 int launch_attn_sm100(const xdit_attn_params& p, cudaStream_t stream);
 
+// ---- attention prologue (prologue.cu) ------------------------------------------------------------
+int launch_prologue(const xdit_prologue_params& p, cudaStream_t stream);
+
 }  // namespace xdit

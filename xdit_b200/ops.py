@@ -280,5 +280,52 @@ def merge_out_lse(o_acc: torch.Tensor, lse_acc: torch.Tensor, out_b: torch.Tenso
     launch_count += 1
 
 
+def qk_norm_rope_pack(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, heads: int, dst_q: torch.Tensor,
+                      dst_k: torch.Tensor, dst_v: torch.Tensor, peer_strides: Sequence[int], U: int = 1, *,
+                      norm_q_weight: Optional[torch.Tensor] = None, norm_k_weight: Optional[torch.Tensor] = None,
+                      eps: float = 1e-6, norm_per_head: bool = False, cos: Optional[torch.Tensor] = None,
+                      sin: Optional[torch.Tensor] = None) -> None:
+    """RMSNorm(q, k) + rotary embedding + head split + Ulysses pack in one launch (``xdit_qk_norm_rope_pack``).
+
+    ``q, k, v``: projections ``[B, s, heads*D]`` (any batch/row strides, e.g. column slices of a fused
+    qkv projection).  ``dst_*``: 1-D tensors positioned at the tensor's slot inside peer 0's block of
+    the send buffer, ``peer_strides`` the distance in elements between two peers' blocks.  ``cos, sin``:
+    fp32 ``[s, D]``.
+    """
+    global launch_count
+    _require_cuda(q, k, v, dst_q, dst_k, dst_v, norm_q_weight, norm_k_weight, cos, sin)
+    B, s, HD = q.shape
+    if HD % heads or k.shape != q.shape or v.shape != q.shape:
+        raise ValueError("q, k and v must be [B, s, heads*D] of one shape")
+    if q.stride(2) != 1 or k.stride(2) != 1 or v.stride(2) != 1:
+        raise ValueError("the hidden axis must be contiguous")
+    D = HD // heads
+    for w in (norm_q_weight, norm_k_weight):
+        if w is not None and (w.dtype != q.dtype or not w.is_contiguous() or w.numel() != (D if norm_per_head else HD)):
+            raise ValueError("norm weights must be contiguous, in the tensors' dtype, [D] per head or [heads*D]")
+    if (cos is None) != (sin is None):
+        raise ValueError("cos and sin go together")
+    if cos is not None:
+        if cos.dtype != torch.float32 or sin.dtype != torch.float32 or cos.shape != (s, D) or sin.shape != (s, D):
+            raise ValueError("cos and sin must be fp32 [s, D]")
+        if cos.stride(1) != 1 or sin.stride(1) != 1 or cos.stride(0) != sin.stride(0):
+            raise ValueError("cos and sin need contiguous rows of equal stride")
+    p = _capi.PrologueParams(
+        dtype=_dtype(q), B=B, H=heads, D=D, s=s, U=U, norm_per_head=int(bool(norm_per_head)), eps=float(eps),
+        q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(),
+        q_stride_b=q.stride(0), q_stride_row=q.stride(1), k_stride_b=k.stride(0), k_stride_row=k.stride(1),
+        v_stride_b=v.stride(0), v_stride_row=v.stride(1),
+        norm_q_weight=norm_q_weight.data_ptr() if norm_q_weight is not None else None,
+        norm_k_weight=norm_k_weight.data_ptr() if norm_k_weight is not None else None,
+        cos=cos.data_ptr() if cos is not None else None, sin=sin.data_ptr() if sin is not None else None,
+        cos_sin_stride_row=cos.stride(0) if cos is not None else 0,
+        dst_q=dst_q.data_ptr(), dst_k=dst_k.data_ptr(), dst_v=dst_v.data_ptr(),
+        dst_q_peer_stride=int(peer_strides[0]), dst_k_peer_stride=int(peer_strides[1]),
+        dst_v_peer_stride=int(peer_strides[2]))
+    with torch.cuda.device(q.device):
+        _capi.check(_capi.load().xdit_qk_norm_rope_pack(C.byref(p), _stream(q)), "xdit_qk_norm_rope_pack")
+    launch_count += 1
+
+
 def default_scale(D: int) -> float:
     return 1.0 / math.sqrt(D)
