@@ -310,19 +310,27 @@ def run_workload(torch, dist, xdit_b200, ops, name, w, args, device, rank, world
 
 def hbm_kernels(torch, ops, device, hbm_peak, peak_kind):
     """Achieved HBM GB/s (algorithmic bytes = read + write of the moved rows) of the HBM-bound
-    kernels at the shapes of the configs, CUDA events, 512 MB written between repeats to flush L2."""
+    kernels at the shapes of the configs, CUDA events around four back-to-back launches, 512 MB written
+    between repeats to flush L2."""
     flush = torch.empty(512 << 20, dtype=torch.uint8, device=device)
 
-    def timeit(fn, reps=10):
+    def timeit(fn, reps=10, inner=4):
+        # `inner` launches back to back between the events: the host-side cost of one call (tens of
+        # microseconds of Python and ctypes) would otherwise sit inside the measured interval while the
+        # GPU idles.  The tensors of one call are larger than L2 or are flushed by the call before it.
         ts = []
         for _ in range(3):
             fn()
         for _ in range(reps):
             flush.fill_(1)
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(); fn(); e1.record()
+            fn()  # queue depth: the timed launches below are issued while this one runs
+            e0.record()
+            for _ in range(inner):
+                fn()
+            e1.record()
             torch.cuda.synchronize(device)
-            ts.append(e0.elapsed_time(e1))
+            ts.append(e0.elapsed_time(e1) / inner)
         ts.sort()
         return ts[len(ts) // 2] * 1e-3
 
@@ -338,6 +346,19 @@ def hbm_kernels(torch, ops, device, hbm_peak, peak_kind):
     nbytes = 2 * 3 * H * s * D * 2
     res["ulysses_pack_wan_qkv"] = {"bytes": nbytes, "ms": t * 1e3, "achieved": nbytes / t / 1e9}
     del srcs, send
+    # fused prologue on the same shard: RMSNorm(q, k) over 5120 + rotary embedding + head split + pack of
+    # the three [1, 9450, 5120] projections of a Wan layer (plus the fp32 cos/sin rows of a token)
+    proj = [torch.randn(1, s, H * D, device=device, dtype=bf) for _ in range(3)]
+    wn = torch.ones(H * D, device=device, dtype=bf)
+    ang = torch.randn(s, D // 2, device=device)
+    cs, sn = ang.cos().repeat_interleave(2, 1).contiguous(), ang.sin().repeat_interleave(2, 1).contiguous()
+    send = torch.empty(3 * U * blk, dtype=bf, device=device)
+    t = timeit(lambda: ops.qk_norm_rope_pack(proj[0], proj[1], proj[2], H, send, send[blk:], send[2 * blk:],
+                                             (3 * blk, 3 * blk, 3 * blk), U, norm_q_weight=wn, norm_k_weight=wn,
+                                             cos=cs, sin=sn))
+    nbytes = 2 * 3 * H * s * D * 2 + 2 * 2 * s * D * 4
+    res["qk_norm_rope_pack_wan"] = {"bytes": nbytes, "ms": t * 1e3, "achieved": nbytes / t / 1e9}
+    del proj, send
     # PipeFusion stale-KV patch, PixArt-Sigma 2048^2: 2048 fresh rows of 16 x 72 into 16384-row caches
     kc = torch.zeros(1, 16, 16384, 72, dtype=bf, device=device)
     vc = torch.zeros_like(kc)
@@ -367,12 +388,17 @@ def hbm_kernels(torch, ops, device, hbm_peak, peak_kind):
 # DiT step latency on random-init stand-ins of the named architectures (plain torch bf16 for
 # everything but attention; no checkpoint or diffusers is available here)
 # --------------------------------------------------------------------------------------------
-def dit_step_latency(torch, dist, xdit_b200, kind, device, rank, world, reps=5):
+def dit_step_latency(torch, dist, xdit_b200, kind, device, rank, world, reps=5, fused_prologue=True):
     """One transformer forward (= one denoising step) of a Flux.1-dev-shaped MMDiT or a
-    Wan2.1-14B-shaped video DiT: QKV/out projections, q/k RMS-norm, RoPE, MLPs and norms in torch
-    bf16 with N(0, 0.02) weights, attention through ``xdit_b200.USP`` (text cross-attention through
-    ``xdit_b200.attention``), the sequence sharded over the ranks.  Returns milliseconds (median)."""
+    Wan2.1-14B-shaped video DiT: QKV/out projections, MLPs and norms in torch bf16 with N(0, 0.02)
+    weights, the sequence sharded over the ranks.  Self-attention from the projections on: with
+    ``fused_prologue`` through ``xdit_b200.prologue.attention_from_projections`` (q/k RMS-norm, rotary
+    embedding, head split and pack in one kernel), otherwise q/k RMS-norm and rotary embedding in
+    torch and ``xdit_b200.USP``, the way the reference's processors are written.  Text cross-attention
+    through ``xdit_b200.attention``.  Returns milliseconds (median)."""
     import torch.nn.functional as F
+
+    from xdit_b200.prologue import attention_from_projections
 
     bf = torch.bfloat16
     w = WORKLOADS[kind]
@@ -388,18 +414,32 @@ def dit_step_latency(torch, dist, xdit_b200, kind, device, rank, world, reps=5):
     def lin(i, o):
         return torch.randn(o, i, device=device, dtype=torch.float32, generator=g).mul_(0.02).to(bf)
 
-    def rms(x):  # over head_dim
-        return x * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-6).to(x.dtype)
+    per_head = kind == "flux"  # Flux normalises q and k per head, Wan over all heads of a token
+    wq = (1 + 0.1 * torch.randn(D if per_head else hid, device=device, generator=g)).to(bf)
+    wk = (1 + 0.1 * torch.randn(D if per_head else hid, device=device, generator=g)).to(bf)
+    ang = torch.randn(s, D // 2, device=device, generator=g)
+    cos = ang.cos().repeat_interleave(2, 1).contiguous()  # fp32 [s, D], each frequency twice
+    sin = ang.sin().repeat_interleave(2, 1).contiguous()
+    rotary = (cos[None, :, None, :], sin[None, :, None, :])
 
-    cos = torch.randn(1, s, 1, D // 2, device=device, generator=g).cos().to(bf)
-    sin = torch.randn(1, s, 1, D // 2, device=device, generator=g).sin().to(bf)
+    def rope(x):  # x [B, s, H, D], interleaved pairs as in the reference's Wan processor
+        x1, x2 = x.unflatten(-1, (-1, 2)).unbind(-1)
+        out = torch.empty_like(x)
+        out[..., 0::2] = x1 * rotary[0][..., 0::2] - x2 * rotary[1][..., 1::2]
+        out[..., 1::2] = x1 * rotary[1][..., 1::2] + x2 * rotary[0][..., 0::2]
+        return out
 
-    def rope(x):  # x [B, s, H, D]
-        x1, x2 = x[..., : D // 2], x[..., D // 2:]
-        return torch.cat([x1 * cos - x2 * sin, x1 * sin + x2 * cos], -1)
-
-    def attn(q, k, v):  # [B, s, H, D] -> [B, s, H*D]
-        o = xdit_b200.USP(rope(rms(q)).transpose(1, 2), rope(rms(k)).transpose(1, 2), v.transpose(1, 2))
+    def attn(q, k, v):  # [B, s, H, D] views of the projections -> [B, s, H*D]
+        if fused_prologue:
+            return attention_from_projections(q.reshape(1, s, hid), k.reshape(1, s, hid), v.reshape(1, s, hid), H,
+                                              norm_q_weight=wq, norm_k_weight=wk, eps=1e-6, norm_per_head=per_head,
+                                              rotary_emb=rotary)
+        if per_head:
+            q, k = F.rms_norm(q, (D,), wq, 1e-6), F.rms_norm(k, (D,), wk, 1e-6)
+        else:
+            q = F.rms_norm(q.reshape(1, s, hid), (hid,), wq, 1e-6).view(1, s, H, D)
+            k = F.rms_norm(k.reshape(1, s, hid), (hid,), wk, 1e-6).view(1, s, H, D)
+        o = xdit_b200.USP(rope(q).transpose(1, 2), rope(k).transpose(1, 2), v.transpose(1, 2))
         return o.transpose(1, 2).reshape(1, s, hid)
 
     x = torch.randn(1, s, hid, device=device, generator=g).to(bf)
@@ -461,7 +501,9 @@ def dit_step_latency(torch, dist, xdit_b200, kind, device, rank, world, reps=5):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     return {"ms_per_step": ms, "ulysses": U, "ring": R, "reps": reps,
-            "what": "one forward of a random-init stand-in (torch bf16 linears/norms/RoPE + xdit_b200 attention)"}
+            "what": "one forward of a random-init stand-in (torch bf16 linears/norms/MLPs + xdit_b200 attention; "
+                    + ("q/k norm + rotary embedding + head split fused with the pack" if fused_prologue
+                       else "q/k norm and rotary embedding in torch, as the reference's processors do") + ")"}
 
 
 def cpu_baseline(w):
@@ -570,8 +612,12 @@ def main():
             extra["dit_step"] = {}
             for kind in (("flux", "wan") if args.dit == "both" else (args.dit,)):
                 try:
-                    extra["dit_step"][kind] = dit_step_latency(torch, dist, xdit_b200, kind, device, rank, world,
-                                                               reps=5 if kind == "flux" else 3)
+                    reps = 5 if kind == "flux" else 3
+                    r_f = dit_step_latency(torch, dist, xdit_b200, kind, device, rank, world, reps=reps)
+                    r_t = dit_step_latency(torch, dist, xdit_b200, kind, device, rank, world, reps=reps,
+                                           fused_prologue=False)
+                    r_f["ms_per_step_torch_prologue"] = r_t["ms_per_step"]
+                    extra["dit_step"][kind] = r_f
                 except Exception as e:
                     extra["dit_step"][kind] = {"error": repr(e)[:200]}
                 torch.cuda.empty_cache()

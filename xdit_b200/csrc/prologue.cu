@@ -14,6 +14,7 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kMaxVec = 4;  // vectors of 8 elements per thread: H*D <= 8192
+constexpr int kRowRun = 8;
 
 template <typename T> struct Cvt;
 template <> struct Cvt<__nv_bfloat16> {
@@ -63,8 +64,27 @@ __global__ void __launch_bounds__(kThreads) qk_norm_rope_pack_kernel(const __gri
   const int Hl = a.H / a.U;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t rows = (int64_t)a.B * a.s;
-  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+  const bool same_col = kThreads % vpd == 0;
+  // a CTA takes runs of kRowRun consecutive token rows: its 256-byte writes to one head then fall
+  // next to each other and leave L2 as longer runs
+  const int64_t nruns = (rows + kRowRun - 1) / kRowRun;
+  for (int64_t run = blockIdx.x; run < nruns; run += gridDim.x)
+  for (int64_t r = run * kRowRun; r < min(rows, (run + 1) * kRowRun); ++r) {
     const int b = (int)(r / a.s), row = (int)(r - (int64_t)b * a.s);
+    // With D/8 dividing the block size every vector of a thread starts at the same column of its head,
+    // so the thread needs one set of eight cos and sin values per token row for q and k alike.
+    float cs_row[8], sn_row[8];
+    if (same_col && a.cos != nullptr) {
+      const int d0 = (threadIdx.x % vpd) * 8;
+      const float* cr = a.cos + (int64_t)row * a.cs_stride_row + d0;
+      const float* sr = a.sin + (int64_t)row * a.cs_stride_row + d0;
+      const float4 c0 = __ldg(reinterpret_cast<const float4*>(cr)), c1 = __ldg(reinterpret_cast<const float4*>(cr) + 1);
+      const float4 s0 = __ldg(reinterpret_cast<const float4*>(sr)), s1 = __ldg(reinterpret_cast<const float4*>(sr) + 1);
+      cs_row[0] = c0.x; cs_row[1] = c0.y; cs_row[2] = c0.z; cs_row[3] = c0.w;
+      cs_row[4] = c1.x; cs_row[5] = c1.y; cs_row[6] = c1.z; cs_row[7] = c1.w;
+      sn_row[0] = s0.x; sn_row[1] = s0.y; sn_row[2] = s0.z; sn_row[3] = s0.w;
+      sn_row[4] = s1.x; sn_row[5] = s1.y; sn_row[6] = s1.z; sn_row[7] = s1.w;
+    }
 #pragma unroll 1
     for (int tns = 0; tns < 3; ++tns) {
       const char* src = a.src[tns] + b * a.src_stride_b[tns] + row * a.src_stride_row[tns];
@@ -151,12 +171,18 @@ __global__ void __launch_bounds__(kThreads) qk_norm_rope_pack_kernel(const __gri
             }
           }
           if (rope) {
-            const float* cr = a.cos + (int64_t)row * a.cs_stride_row + d0;
-            const float* sr = a.sin + (int64_t)row * a.cs_stride_row + d0;
-            const float4 c0 = __ldg(reinterpret_cast<const float4*>(cr)), c1 = __ldg(reinterpret_cast<const float4*>(cr) + 1);
-            const float4 s0 = __ldg(reinterpret_cast<const float4*>(sr)), s1 = __ldg(reinterpret_cast<const float4*>(sr) + 1);
-            const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-            const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+            float cs[8], sn[8];
+            if (same_col) {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) { cs[e] = cs_row[e]; sn[e] = sn_row[e]; }
+            } else {
+              const float* cr = a.cos + (int64_t)row * a.cs_stride_row + d0;
+              const float* sr = a.sin + (int64_t)row * a.cs_stride_row + d0;
+              const float4 c0 = __ldg(reinterpret_cast<const float4*>(cr)), c1 = __ldg(reinterpret_cast<const float4*>(cr) + 1);
+              const float4 s0 = __ldg(reinterpret_cast<const float4*>(sr)), s1 = __ldg(reinterpret_cast<const float4*>(sr) + 1);
+              cs[0] = c0.x; cs[1] = c0.y; cs[2] = c0.z; cs[3] = c0.w; cs[4] = c1.x; cs[5] = c1.y; cs[6] = c1.z; cs[7] = c1.w;
+              sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
+            }
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               // pair (x1, x2) = elements (2e, 2e+1); cosine taken at the even, sine at the odd column
@@ -207,7 +233,8 @@ int launch_prologue(const xdit_prologue_params& p, cudaStream_t stream) {
   int rc = check_device(&sms);
   if (rc) return rc;
   const int64_t rows = (int64_t)p.B * p.s;
-  const int grid = (int)(rows < (int64_t)sms * 8 ? rows : (int64_t)sms * 8);
+  const int64_t nruns = (rows + kRowRun - 1) / kRowRun;
+  const int grid = (int)(nruns < (int64_t)sms * 8 ? nruns : (int64_t)sms * 8);
   if (p.dtype == XDIT_BF16) qk_norm_rope_pack_kernel<__nv_bfloat16><<<grid, kThreads, 0, stream>>>(a);
   else qk_norm_rope_pack_kernel<__half><<<grid, kThreads, 0, stream>>>(a);
   cudaError_t e = cudaGetLastError();
