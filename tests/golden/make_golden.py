@@ -1,10 +1,9 @@
 #!/usr/bin/env python
 """Generate the golden fixtures in this directory by running the *unmodified* xDiT reference.
 
-Run once, in a container that has the reference checkout (default ``/root/reference``,
-override with ``XDIT_REFERENCE``)::
+Run once, where a checkout of the reference is available; ``XDIT_REFERENCE`` names its root::
 
-    python tests/golden/make_golden.py
+    XDIT_REFERENCE=<path to the xDiT checkout> python tests/golden/make_golden.py
 
 The reference's ``xfuser/model_executor/layers/usp.py`` and
 ``xfuser/core/cache_manager/cache_manager.py`` are imported as they are.  Their heavy
@@ -31,7 +30,9 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = os.environ.get("XDIT_REFERENCE", "/root/reference")
+REF = os.environ.get("XDIT_REFERENCE", "")
+if not os.path.isdir(os.path.join(REF, "xfuser")):
+    raise SystemExit("set XDIT_REFERENCE to the root of an xDiT checkout (the directory that holds xfuser/)")
 
 
 # --------------------------------------------------------------------------------------

@@ -6,7 +6,7 @@ import torch
 
 import os
 
-from tests.usp_worker import HERE, golden_files, run, run_kv
+from tests.usp_worker import HERE, golden_files, run, run_kv, run_prologue
 
 pytestmark = pytest.mark.gpu
 
@@ -35,3 +35,11 @@ def test_four_gpus(mode, dtype, tol):
 def test_stale_kv_under_ulysses_two_gpus(dtype, tol):
     _need(2)
     run_kv(2, os.path.join(HERE, "golden", "uspkv_u2r1.npz"), 29770, backend="nccl", dtype_name=dtype, tol=tol)
+
+
+@pytest.mark.parametrize("U,R", [(2, 1), (1, 2)])
+def test_attention_from_projections_two_gpus(U, R):
+    """The processor slice with the fused prologue kernel: Ulysses 2 writes the projections straight into
+    the all-to-all send buffer, ring 2 hands [B,H,s,D] tensors to the ring path."""
+    _need(2)
+    run_prologue(2, U, R, 29780 + R, backend="nccl", dtype_name="bfloat16", tol=3e-2)

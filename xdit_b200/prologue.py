@@ -75,6 +75,15 @@ def attention_from_projections(query: torch.Tensor, key: torch.Tensor, value: to
         raise ValueError("hidden size must be divisible by the number of heads")
     D = HD // heads
     U, R = get_ulysses_parallel_world_size(), get_ring_parallel_world_size()
+    if U == 1 and R == 1:
+        # one GPU: the attention kernel writes its rows straight into [B, s, heads, D], which is the
+        # head-merged tensor the output projection takes
+        q, k, v = qk_norm_rope_heads(query, key, value, heads, norm_q_weight=norm_q_weight,
+                                     norm_k_weight=norm_k_weight, eps=eps, norm_per_head=norm_per_head,
+                                     rotary_emb=rotary_emb)
+        out = torch.empty(B, s, heads, D, dtype=query.dtype, device=query.device)
+        ops.attn_fwd(q, k, v, out=out.permute(0, 2, 1, 3), scale=softmax_scale)
+        return out.view(B, s, HD)
     if U == 1 or R > 1:
         q, k, v = qk_norm_rope_heads(query, key, value, heads, norm_q_weight=norm_q_weight,
                                      norm_k_weight=norm_k_weight, eps=eps, norm_per_head=norm_per_head,
