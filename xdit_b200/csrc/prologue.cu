@@ -56,7 +56,7 @@ struct PrologueArgs {
 };
 
 template <typename T>
-__global__ void __launch_bounds__(kThreads) qk_norm_rope_pack_kernel(const __grid_constant__ PrologueArgs a) {
+__global__ void __launch_bounds__(kThreads, 3) qk_norm_rope_pack_kernel(const __grid_constant__ PrologueArgs a) {
   __shared__ float red[kThreads / 32];
   const int HD = a.H * a.D;
   const int nvec = HD / 8;
@@ -65,12 +65,25 @@ __global__ void __launch_bounds__(kThreads) qk_norm_rope_pack_kernel(const __gri
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t rows = (int64_t)a.B * a.s;
   const bool same_col = kThreads % vpd == 0;
+  // Which head, column and destination slot a thread's k-th vector belongs to does not depend on the
+  // token row: the integer divisions are done once here, not per vector and row.
+  int d0_k[kMaxVec], peer_k[kMaxVec];
+  int64_t slot_k[kMaxVec];  // byte offset of (head in peer, column) inside a peer block, row 0 of batch 0
+#pragma unroll
+  for (int k = 0; k < kMaxVec; ++k) {
+    const int idx = threadIdx.x + k * kThreads;
+    const int head = idx / vpd;
+    d0_k[k] = (idx - head * vpd) * 8;
+    peer_k[k] = head / Hl;
+    slot_k[k] = ((int64_t)(head - peer_k[k] * Hl) * a.B * a.s * a.D + d0_k[k]) * 2;
+  }
   // a CTA takes runs of kRowRun consecutive token rows: its 256-byte writes to one head then fall
   // next to each other and leave L2 as longer runs
   const int64_t nruns = (rows + kRowRun - 1) / kRowRun;
   for (int64_t run = blockIdx.x; run < nruns; run += gridDim.x)
   for (int64_t r = run * kRowRun; r < min(rows, (run + 1) * kRowRun); ++r) {
     const int b = (int)(r / a.s), row = (int)(r - (int64_t)b * a.s);
+    const int64_t row_off = ((int64_t)b * a.s + row) * a.D * 2;  // bytes from a head's first row to this one
     // With D/8 dividing the block size every vector of a thread starts at the same column of its head,
     // so the thread needs one set of eight cos and sin values per token row for q and k alike.
     float cs_row[8], sn_row[8];
@@ -150,7 +163,7 @@ __global__ void __launch_bounds__(kThreads) qk_norm_rope_pack_kernel(const __gri
       for (int k = 0; k < kMaxVec; ++k) {
         const int idx = threadIdx.x + k * kThreads;
         if (idx >= nvec) continue;
-        const int head = idx / vpd, d0 = (idx - head * vpd) * 8;
+        const int d0 = d0_k[k];
         uint4 o = v[k];
         if (norm || rope) {
           float x[8];
@@ -196,9 +209,7 @@ __global__ void __launch_bounds__(kThreads) qk_norm_rope_pack_kernel(const __gri
           o.z = Cvt<T>::pack(x[4], x[5]);
           o.w = Cvt<T>::pack(x[6], x[7]);
         }
-        const int p = head / Hl, hl = head - p * Hl;
-        char* d = a.dst[tns] + p * a.dst_peer_stride[tns] +
-                  ((((int64_t)hl * a.B + b) * a.s + row) * a.D + d0) * 2;
+        char* d = a.dst[tns] + peer_k[k] * a.dst_peer_stride[tns] + slot_k[k] + row_off;
         *reinterpret_cast<uint4*>(d) = o;
       }
     }
