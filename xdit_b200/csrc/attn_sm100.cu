@@ -48,10 +48,6 @@ constexpr int kThreads = 384;  // 8 softmax warps, MMA warp, TMA warp, 2 idle wa
 constexpr int kSlabBytes = kTile * 128;       // one 64-element slab of a 128-row tile
 constexpr int kBoxBytes = kChunk * 128;       // one TMA box: 64 rows x 64 elements
 constexpr uint32_t kWaitLimitNs = 200000000u;  // 0.2 s: no legitimate wait comes near this
-#ifndef XDIT_EMU_PAIRS
-#define XDIT_EMU_PAIRS 0
-#endif
-constexpr int kEmuPairs = XDIT_EMU_PAIRS;  // of every 4 column pairs, how many take the polynomial exp2
 
 struct alignas(64) Sm100Args {
   CUtensorMap tm_q, tm_k, tm_v, tm_k2, tm_v2;
@@ -140,12 +136,6 @@ __device__ __forceinline__ void tc_mma_ss(uint32_t d_tmem, uint64_t adesc, uint6
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc) : "memory");
 }
-__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(acc) : "memory");
-}
 // One lane of a converged warp.
 __device__ __forceinline__ bool elect_one() {
   uint32_t pred;
@@ -227,9 +217,6 @@ __device__ __forceinline__ void pv_block4(uint32_t d_tmem, uint32_t p_tmem, uint
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ float ex2(float x) {
-#ifdef XDIT_EXP_NOEX2
-  return x * 0.001f + 1.0f;
-#endif
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
@@ -262,13 +249,9 @@ __device__ __forceinline__ float ex2_ordered(float x) {
   return y;
 }
 __device__ __forceinline__ float max3(float a, float b, float c) {
-#ifdef XDIT_EXP_MAX2
-  return fmaxf(a, fmaxf(b, c));
-#else
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
   return d;
-#endif
 }
 // packed fp32 pairs (one 64-bit register): halves the issue slots of the softmax arithmetic
 __device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
@@ -289,32 +272,6 @@ __device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
   return d;
 }
-// 2^x for a pair on the FMA/ALU pipes instead of the special-function unit: x = n + f with
-// n = round(x) taken from the mantissa of x + 1.5*2^23, 2^f by a cubic (relative error 7.5e-5,
-// far below the 16-bit P it feeds), n added into the exponent field.  x is clamped at -126 so
-// that the exponent field cannot wrap.
-__device__ __forceinline__ uint64_t ex2_emu2(uint64_t x2) {
-  float x0, x1;
-  f2_unpack(x2, x0, x1);
-  x0 = fmaxf(x0, -126.f);
-  x1 = fmaxf(x1, -126.f);
-  const uint64_t xc = f2_pack(x0, x1);
-  const uint64_t magic = f2_pack(12582912.f, 12582912.f);
-  const uint64_t t2 = f2_add(xc, magic);
-  const uint64_t n2 = f2_add(t2, f2_pack(-12582912.f, -12582912.f));
-  const uint64_t f2 = f2_fma(n2, f2_pack(-1.f, -1.f), xc);
-  uint64_t p2 = f2_fma(f2, f2_pack(0.05517132207751274f, 0.05517132207751274f),
-                       f2_pack(0.24261054396629333f, 0.24261054396629333f));
-  p2 = f2_fma(p2, f2, f2_pack(0.6932609677314758f, 0.6932609677314758f));
-  p2 = f2_fma(p2, f2, f2_pack(0.9999281167984009f, 0.9999281167984009f));
-  float p0, p1, t0, t1;
-  f2_unpack(p2, p0, p1);
-  f2_unpack(t2, t0, t1);
-  p0 = __uint_as_float(__float_as_uint(p0) + (__float_as_uint(t0) << 23));
-  p1 = __uint_as_float(__float_as_uint(p1) + (__float_as_uint(t1) << 23));
-  return f2_pack(p0, p1);
-}
-
 // Shared-memory matrix descriptors (sm_100 format: version 1 at bit 46, 128-byte swizzle = 2 at
 // bits 61-63, offsets in 16-byte units).
 // K-major operand (Q, K): rows of 128 bytes, 8-row groups 1024 bytes apart.
@@ -337,12 +294,6 @@ __device__ __forceinline__ uint32_t make_idesc(bool bf16, bool b_mn_major, int n
 
 template <bool BF16>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
-#ifdef XDIT_EXP_PRMT_PACK
-  if constexpr (BF16) {
-    // round-half-up to bf16 on the integer pipe: add half an ulp, keep the upper 16 bits
-    return __byte_perm(__float_as_uint(lo) + 0x8000u, __float_as_uint(hi) + 0x8000u, 0x7632);
-  }
-#endif
   if constexpr (BF16) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -707,11 +658,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_sm100_kernel(const __gri
           m_run = m_new;
         }
       }
-      // P = 2^(s*scale - m): in every group of 8 columns kEmuPairs pairs go through the
-      // polynomial on the FMA pipe and the rest through ex2 on the special-function unit.
-      // P is handed to the tensor core in two halves of 64 key columns.
+      // P = 2^(s*scale - m), handed to the tensor core in two halves of 64 key columns.
       const uint64_t sl2_2 = f2_pack(sl2, sl2), negm_2 = f2_pack(-m_run, -m_run);
-#if XDIT_EMU_PAIRS == 0
       // Software-pipelined in blocks of 16 columns: the 16 ex2 of block b+1 are issued before the
       // results of block b are consumed.  A warp issues in order, so without this every pair
       // would wait out the special-function unit's latency before the next one starts.
@@ -761,44 +709,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_sm100_kernel(const __gri
         f2_unpack(f2_add(f2_add(acc4[0], acc4[1]), f2_add(acc4[2], acc4[3])), a0, a1);
         l_run += a0 + a1;
       }
-#else
-      uint64_t sum_a = f2_pack(0.f, 0.f), sum_b = sum_a;
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t pk[32];
-#pragma unroll
-        for (int c = 64 * half; c < 64 * half + 64; c += 8) {
-#pragma unroll
-          for (int pr = 0; pr < 4; ++pr) {
-            const int e = c + 2 * pr;
-            uint64_t x2 = f2_fma(f2_pack(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), sl2_2, negm_2);
-            uint64_t p2;
-            if (pr < kEmuPairs) {
-              p2 = ex2_emu2(x2);
-            } else {
-              float x0, x1;
-              f2_unpack(x2, x0, x1);
-              p2 = f2_pack(ex2(x0), ex2(x1));
-            }
-            if (pr & 1) sum_b = f2_add(sum_b, p2); else sum_a = f2_add(sum_a, p2);
-            float p0, p1;
-            f2_unpack(p2, p0, p1);
-            pk[(e - 64 * half) / 2] = pack2<BF16>(p0, p1);
-          }
-        }
-        if (half == 0) XDIT_TRACE_DEP(t, j, 3, pk[0] ^ pk[31]);
-        XDIT_TMEM_ST32(pk, 0, tmem_s + 32 * half);
-        tmem_wait_st();
-        tc_fence_before();
-        mbar_arrive(bar_p_full(t, half));
-        if (half == 0) XDIT_TRACE(t, j, 4);
-      }
-      {
-        float a0, a1;
-        f2_unpack(f2_add(sum_a, sum_b), a0, a1);
-        l_run += a0 + a1;
-      }
-#endif
       XDIT_TRACE(t, j, 5);
       return true;
     };
@@ -806,11 +716,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_sm100_kernel(const __gri
       for (int j = 0; j < n_tiles; ++j) {
         ok = __all_sync(0xffffffffu, mbar_wait(bar_s_full(t), j & 1, abort_flag, 300 + t));
         if (!ok) break;
-#ifdef XDIT_EXP_NOMASK
-        const int v0 = kChunk, v1 = kChunk;
-#else
         const int v0 = next_valid(), v1 = next_valid();
-#endif
         if (v0 < kChunk || v1 < kChunk) softmax_tile(std::true_type{}, j, v0, v1);
         else softmax_tile(std::false_type{}, j, v0, v1);
       }
