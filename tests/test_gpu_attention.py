@@ -247,6 +247,50 @@ def test_reference_test_shape_14867(ops):
     compare(out[:, 5:6, -1500:], want, "tail rows")
 
 
+def test_wan_full_length_ring_split_property(ops):
+    """Wan2.1 sequence length (75,600 tokens, head_dim 128), two heads: attention over all keys equals
+    the epilogue-merged attention over four ring shards of 18,900 keys (the R4 split of the video
+    configuration); selected query rows against the oracle over all 75,600 keys."""
+    B, H, S, D, R = 1, 2, 75600, 128, 4
+    q, k, v = (rand((B, H, S, D), torch.bfloat16, 40 + i) for i in range(3))
+    full, lse_full = _run(ops, q, k, v)
+    o_acc = torch.empty(B, H, S, D, dtype=torch.float32, device="cuda")
+    lse_acc = torch.empty(B, H, S, dtype=torch.float32, device="cuda")
+    ring = torch.empty_like(q)
+    lse_ring = torch.empty_like(lse_full)
+    sh = S // R
+    for i in range(R):
+        ks, vs = k[:, :, i * sh:(i + 1) * sh], v[:, :, i * sh:(i + 1) * sh]
+        last = i == R - 1
+        ops.attn_fwd(q, ks, vs, out=ring if last else None, lse=lse_ring if last else None, o_acc=o_acc,
+                     lse_acc=lse_acc, acc_in=i > 0, acc_out=not last)
+    torch.cuda.synchronize()
+    ops.check_status()
+    compare(ring, np64(full), "four ring shards vs one call", max_abs=1e-2)
+    compare(lse_ring, np64(lse_full), "lse", max_abs=1e-3, cos=0.0)
+    for rows in (slice(0, 96), slice(37777, 37777 + 96), slice(S - 96, S)):
+        want, want_lse = oracle_attn(q[:, :, rows], k, v)
+        compare(full[:, :, rows], want, f"rows {rows.start} vs oracle")
+        assert np.abs(np64(lse_full[:, :, rows]) - want_lse).max() < 2e-3
+
+
+def test_hunyuan_full_length_joint_rear_property(ops):
+    """HunyuanVideo sequence length (118,800 image + 256 text tokens, joint "rear"), one head: the text
+    keys as the kernel's second key/value source equal a concatenated key tensor; selected rows
+    against the oracle."""
+    B, H, S, Sj, D = 1, 1, 118800, 256, 128
+    q, k, v = (rand((B, H, S, D), torch.bfloat16, 50 + i) for i in range(3))
+    jk, jv = rand((B, H, Sj, D), torch.bfloat16, 60), rand((B, H, Sj, D), torch.bfloat16, 61)
+    out2, _ = _run(ops, q, k, v, jk, jv)
+    cat, _ = _run(ops, q, torch.cat([k, jk], 2), torch.cat([v, jv], 2))
+    torch.cuda.synchronize()
+    ops.check_status()
+    compare(out2, np64(cat), "second source vs concatenated keys", max_abs=2e-3)
+    rows = slice(59000, 59064)
+    want, _ = oracle_attn(q[:, :, rows], k, v, jk, jv)
+    compare(out2[:, :, rows], want, "rows vs oracle")
+
+
 def test_cuda_graph_replay_matches_eager(ops):
     """A captured step (several USP calls) replays to the same bits as the eager calls."""
     import xdit_b200
