@@ -16,7 +16,7 @@ the results read back, copies inside the timed region.
 N > 1 is launched by ``torch.distributed.run`` (one rank per GPU, NCCL); the sequence is sharded
 over N ranks (strong scaling) with Ulysses degree N, which is the fastest split behind NVSwitch
 (measured at 8 GPUs on the 75.6K workload: U8 7755, U4xR2 7438, U2xR4 6872, R8 6046 TFLOP/s);
-``--sp ULYSSESxRING`` selects another split, e.g. ``--sp 2x4`` for BASELINE config 3's degrees.
+``--sp ULYSSESxRING`` selects another split, e.g. ``--sp 2x4`` for Ulysses 2 x ring 4, the split the Wan2.1 workload is usually quoted with.
 
 ``--impl reference`` times the CPU restatement of the reference's algorithm (the oracle) on the
 host cores of rank 0, on a bounded sample (a subset of heads) of the same workload.

@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define XDIT_ABI_VERSION 1
+#define XDIT_ABI_VERSION 2
 
 #if defined(__GNUC__)
 #define XDIT_API __attribute__((visibility("default")))
@@ -44,7 +44,7 @@ enum xdit_status {
   XDIT_E_ALIGN = -3,              /* a pointer or stride breaks an alignment rule */
   XDIT_E_DTYPE = -4,              /* unknown or unsupported dtype for this entry point */
   XDIT_E_UNSUPPORTED_DEVICE = -5, /* current device is not sm_100 */
-  XDIT_E_KERNEL_TIMEOUT = -6,     /* a bounded wait inside a kernel gave up (see xdit_attn_status) */
+  XDIT_E_KERNEL_TIMEOUT = -6,     /* a bounded wait inside a kernel gave up (xdit_attn_params.status / status_host) */
   XDIT_E_DRIVER = -7              /* a CUDA driver entry point could not be resolved */
 };
 
@@ -85,7 +85,9 @@ struct xdit_seq {
  *   acc_in  != 0 : merge this call's (out,lse) into (o_acc,lse_acc) read from memory;
  *   acc_out != 0 : write the (merged) result to (o_acc,lse_acc) in fp32, leave `out` untouched;
  *   acc_out == 0 : write the (merged) result to `out` in `dtype` (and to `lse` when not NULL).
- * causal != 0 masks key j > query i (top-left aligned), one segment only. */
+ * causal != 0 masks key j > query i (top-left aligned, the torch SDPA convention; flash-attn
+ * aligns bottom-right, which differs when Sq != Sk), one segment only.
+ * B and H are grid dimensions and must not exceed 65535. */
 struct xdit_attn_params {
   int32_t dtype; /* xdit_dtype of q,k,v,out */
   int32_t B, H, D;
@@ -102,6 +104,21 @@ struct xdit_attn_params {
   float softmax_scale; /* <= 0 selects D^-1/2 */
   int32_t force_generic; /* != 0: use the CUDA-core kernel even where the tcgen05 kernel applies */
   int32_t* status;       /* optional device int32: set non-zero when a bounded wait gave up */
+  /* Failure reporting without polling.  Every wait inside the tcgen05 kernel is bounded in time
+   * (wait_limit_ns; 0 selects 0.2 s).  When one runs out the launch drains, frees its TMEM, sets
+   * *status (device) and, when status_host is given, the same code in *status_host: a 4-byte word
+   * in pinned, device-mapped host memory (cudaHostAlloc) that the kernel only ever writes.  While
+   * *status is non-zero later launches do no work, so that one failure does not cost a time limit
+   * per CTA.  xdit_attn_fwd reads *status_host on entry (a plain host load, no synchronisation):
+   * when it is non-zero the call launches nothing and returns XDIT_E_KERNEL_TIMEOUT, until the
+   * caller has cleared both words (cudaMemsetAsync of *status, a store to *status_host).  A caller
+   * that passes only `status` has to read it back itself after a synchronise. */
+  int32_t* status_host;
+  uint32_t wait_limit_ns;
+  /* Test aid for the failure path: != 0 makes the tcgen05 kernel's loader leave the first K/V
+   * stage un-armed, so that the consumer's bounded wait runs out after wait_limit_ns.  The launch
+   * ends normally with the status words set and writes nothing to out. */
+  int32_t selftest_stall;
 };
 XDIT_API int xdit_attn_fwd(const struct xdit_attn_params* p, void* stream);
 /* Which kernel xdit_attn_fwd would run for these parameters: 1 = tcgen05/TMEM/TMA kernel,
@@ -129,7 +146,10 @@ XDIT_API int xdit_attn_which(const struct xdit_attn_params* p);
  *   - every call on a device shares the one array and the array keeps what the last call left.
  *     Nothing needs clearing as long as each sequence starts with acc_in=0, which overwrites the
  *     rows it uses.  Two sequences whose kernels overlap on the GPU (different streams, or
- *     interleaved steps) race on the array: keep one sequence at a time per device. */
+ *     interleaved steps) race on the array: keep one sequence at a time per device;
+ *   - the cached address belongs to the device's primary context: after cudaDeviceReset() it is
+ *     stale and the library does not notice, so a process that resets a device must not call this
+ *     entry point on that device again. */
 #define XDIT_STATIC_ACC_FLOATS (8 * 1024 * 1024)
 XDIT_API int xdit_attn_fwd_static_acc(const struct xdit_attn_params* p, void* stream);
 

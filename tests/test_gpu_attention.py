@@ -52,7 +52,7 @@ def test_generic_kernel(ops, dtype, B, H, Sq, Sk, D, causal):
 
 
 def test_generic_config1_fp32_joint(ops):
-    """BASELINE config 1 as one dense call: 24 heads x 128, 4096 image + 512 joint keys, fp32; a
+    """The Flux-shaped fp32 joint case as one dense call: 24 heads x 128, 4096 image + 512 joint keys; a
     4-head slice keeps the float64 oracle in seconds."""
     B, H, S, Sj, D = 1, 4, 4096, 512, 128
     q = rand((B, H, 600, D), torch.float32, 0)
@@ -317,3 +317,46 @@ def test_cuda_graph_replay_matches_eager(ops):
     ops.check_status()
     for a, b in zip(res, eager):
         assert torch.equal(a, b)
+
+
+def test_timed_out_wait_is_reported_by_the_next_call(ops):
+    """The failure path of the tcgen05 kernel, without any fault: the loader leaves the first K/V
+    stage un-armed (a barrier that nothing completes), the consumer's wait runs out after 2 ms, the
+    launch drains and ends normally with the status words set.  The next launch does no work and the
+    next call through the C ABI returns XDIT_E_KERNEL_TIMEOUT without the caller polling anything;
+    after that the words are clear and the kernel computes again."""
+    from xdit_b200 import _capi
+
+    q, k, v = (rand((1, 2, 256, 128), torch.bfloat16, 40 + i) for i in range(3))
+    assert ops.attn_which(q, k, v) == 1
+    good, _ = _run(ops, q, k, v)
+    sentinel = torch.full_like(q, 7.0)
+    ops.attn_fwd(q, k, v, out=sentinel, _wait_limit_ns=2_000_000, _selftest_stall=True)
+    torch.cuda.synchronize()  # the launch ended by itself: the context is alive
+    st = ops._status(q.device)
+    assert int(st.dev.item()) != 0 and int(st.host.item()) == int(st.dev.item())
+    assert torch.equal(sentinel, torch.full_like(q, 7.0))  # nothing was written
+    with pytest.raises(_capi.XditError) as ei:
+        ops.attn_fwd(q, k, v)
+    assert ei.value.code == -6  # XDIT_E_KERNEL_TIMEOUT
+    assert int(st.dev.item()) == 0 and int(st.host.item()) == 0  # cleared for a retry
+    again, _ = _run(ops, q, k, v)
+    assert torch.equal(again, good)
+
+
+def test_launch_after_a_failure_is_a_no_op_until_cleared(ops):
+    """While the device status word is set, launches exit at once (a failure must not cost one time
+    limit per CTA); check_status() raises, clears, and the kernel runs again."""
+    from xdit_b200 import _capi
+
+    q, k, v = (rand((1, 1, 128, 64), torch.bfloat16, 50 + i) for i in range(3))
+    st = ops._status(q.device)
+    st.dev.fill_(123)  # as a timed-out CTA would leave it; the host word stays clear
+    sentinel = torch.full_like(q, -3.0)
+    ops.attn_fwd(q, k, v, out=sentinel)
+    torch.cuda.synchronize()
+    assert torch.equal(sentinel, torch.full_like(q, -3.0))
+    with pytest.raises(_capi.XditError, match="code 123"):
+        ops.check_status()
+    out, _ = _run(ops, q, k, v)
+    compare(out, oracle_attn(q, k, v)[0], "after clearing")

@@ -167,3 +167,28 @@ def test_merge_matches_oracle(ops, dtype, D):
     # first=True initialises the accumulators from the block
     ops.merge_out_lse(oa, la, ob, lb, first=True)
     assert torch.equal(oa, ob.float()) and torch.equal(la, lb)
+
+
+@pytest.mark.parametrize("dtype,D,rows", [(torch.float32, 72, 150_000), (torch.bfloat16, 96, 120_000),
+                                          (torch.bfloat16, 256, 70_000), (torch.float16, 40, 200_000)])
+def test_merge_many_rows_whose_vectors_span_warps(ops, dtype, D, rows):
+    """Rows of 18, 24, 64 or 10 vectors do not divide a warp, and the launch is several waves of a
+    grid-stride loop: every row's lse must still be read by all of its lanes before it is rewritten.
+    Checked against the oracle's merge on a sample of rows and against a torch restatement on all."""
+    from oracle import usp_oracle as O
+
+    oa = rand((rows, D), torch.float32, 10)
+    la = rand((rows,), torch.float32, 11, scale=3.0)
+    ob = rand((rows, D), dtype, 12)
+    lb = rand((rows,), torch.float32, 13, scale=3.0)
+    oa0, la0 = oa.clone(), la.clone()
+    ops.merge_out_lse(oa, la, ob, lb, first=False)
+    torch.cuda.synchronize()
+    w = torch.sigmoid(lb.double() - la0.double())[:, None]
+    want_all = oa0.double() - w * (oa0.double() - ob.double())
+    assert (oa.double() - want_all).abs().max().item() <= 5e-6
+    idx = torch.arange(0, rows, 997, device="cuda")
+    want_o, want_l = O.merge_out_lse(np64(oa0[idx]).reshape(1, 1, -1, D), np64(la0[idx]).reshape(1, 1, -1),
+                                     np64(ob[idx]).reshape(1, 1, -1, D), np64(lb[idx]).reshape(1, 1, -1))
+    np.testing.assert_allclose(np64(oa[idx]), want_o.reshape(-1, D), atol=2e-6, rtol=1e-5)
+    np.testing.assert_allclose(np64(la[idx]), want_l.reshape(-1), atol=2e-6, rtol=1e-5)

@@ -58,6 +58,7 @@ class AttnParams(C.Structure):
         ("acc_in", C.c_int32), ("acc_out", C.c_int32), ("causal", C.c_int32),
         ("softmax_scale", C.c_float), ("force_generic", C.c_int32),
         ("status", C.c_void_p),
+        ("status_host", C.c_void_p), ("wait_limit_ns", C.c_uint32), ("selftest_stall", C.c_int32),
     ]
 
 

@@ -47,7 +47,7 @@ constexpr int kTile = 128;
 constexpr int kThreads = 384;  // 8 softmax warps, MMA warp, TMA warp, 2 idle warps (full register-trading warpgroup)
 constexpr int kSlabBytes = kTile * 128;       // one 64-element slab of a 128-row tile
 constexpr int kBoxBytes = kChunk * 128;       // one TMA box: 64 rows x 64 elements
-constexpr uint32_t kWaitLimitNs = 200000000u;  // 0.2 s: no legitimate wait comes near this
+constexpr uint32_t kWaitLimitNs = 200000000u;  // default 0.2 s: no legitimate wait comes near this
 
 struct alignas(64) Sm100Args {
   CUtensorMap tm_q, tm_k, tm_v, tm_k2, tm_v2;
@@ -63,10 +63,9 @@ struct alignas(64) Sm100Args {
   float* lse_acc;
   int32_t acc_in, acc_out;
   int32_t* status;
-#ifdef XDIT_DEBUG_DUMP
-  float* dbg_s;  // [2][128][128] raw S of key tile 0 of CTA (0,0,0), then [2][128][128] raw O
-  long long* dbg_t;  // timeline of CTA (0,0,0): [3 roles][64 iterations][8 events] clock64 stamps
-#endif
+  int32_t* status_host;     // optional pinned host word (mapped): written on a timeout only, never read
+  uint32_t wait_limit_ns;   // time limit of every mbarrier wait
+  int32_t selftest_stall;   // test aid: the loader leaves K/V stage 0 un-armed, so a consumer's wait runs out
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -101,13 +100,14 @@ __device__ __forceinline__ uint32_t global_timer_ns() {
 }
 // Bounded wait.  Returns false when the CTA is aborting or the time limit passed (and then
 // raises the abort flag itself, recording `code`).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint32_t limit_ns,
+                                          int code) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint32_t t0 = global_timer_ns();
   for (uint32_t it = 0;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    if ((it & 63) == 63 && global_timer_ns() - t0 > kWaitLimitNs) {
+    if ((it & 63) == 63 && global_timer_ns() - t0 > limit_ns) {
       *abort_flag = code;
       return false;
     }
@@ -222,25 +222,6 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
-#ifdef XDIT_DEBUG_DUMP
-#define XDIT_TRACE(role, it, ev)                                                                   \
-  do {                                                                                             \
-    if (a.dbg_t && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (it) < 64 && lane == 0 && \
-        ((role) == 2 || (warp & 3) == 0))                                                          \
-      a.dbg_t[((role) * 64 + (it)) * 8 + (ev)] = clock64();                                        \
-  } while (0)
-#define XDIT_TRACE_DEP(role, it, ev, dep)                                                          \
-  do {                                                                                             \
-    long long t_;                                                                                  \
-    asm volatile("mov.u64 %0, %%clock64;" : "=l"(t_) : "r"(dep) : "memory");                       \
-    if (a.dbg_t && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (it) < 64 && lane == 0 && \
-        ((role) == 2 || (warp & 3) == 0))                                                          \
-      a.dbg_t[((role) * 64 + (it)) * 8 + (ev)] = t_;                                               \
-  } while (0)
-#else
-#define XDIT_TRACE(role, it, ev) do {} while (0)
-#define XDIT_TRACE_DEP(role, it, ev, dep) do {} while (0)
-#endif
 // same instruction, but volatile: the compiler keeps a run of these in program order, which is how
 // the softmax loop forces a batch of independent ex2 to be issued back to back
 __device__ __forceinline__ float ex2_ordered(float x) {
@@ -427,7 +408,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_sm100_kernel(const __gri
       const int n_items = 2 * n_tiles;
       for (int i = 0; i < n_items && ok; ++i) {
         const int stage = i % NSTAGE;
-        if (i >= NSTAGE) ok = mbar_wait(bar_kv_empty(stage), ((i / NSTAGE) - 1) & 1, abort_flag, 100 + stage);
+        if (a.selftest_stall) { ok = false; break; }  // nothing is armed: the MMA warp's wait on stage 0 runs out
+        if (i >= NSTAGE) ok = mbar_wait(bar_kv_empty(stage), ((i / NSTAGE) - 1) & 1, abort_flag, a.wait_limit_ns, 100 + stage);
         if (!ok) break;
         mbar_arrive_expect_tx(bar_kv_full(stage), L::kStageBytes);
         const int j = i >> 1;
@@ -474,7 +456,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_sm100_kernel(const __gri
       // the low words of the K-major and MN-major forms differ in the leading-offset field only
       constexpr uint32_t v_lo_delta = (uint32_t)((kSlabBytes >> 4) - 1) << 16;
       auto wait_all = [&](uint32_t bar, uint32_t parity, int code) {
-        return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, code));
+        return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, a.wait_limit_ns, code));
       };
       // S_t = Q_t K^T (call from the elected lane only)
       auto issue_qk = [&](int t, int stage) {
@@ -527,9 +509,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_sm100_kernel(const __gri
           ok = wait_all(bar_p_full(t, 0), j & 1, 220 + t);
           if (!ok) break;
           tc_fence_after();
-          if (t == 0) XDIT_TRACE(2, j, 0);
           if (leader) issue_pv_half(t, sv, 0, j == 0);
-          if (t == 0) XDIT_TRACE(2, j, 1);
           if (more && t == 0) {
             // K(j+1) has long arrived; taking the wait here keeps it out of the single-lane region below
             ok = wait_all(bar_kv_full(sk), pk, 230);
@@ -538,7 +518,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_sm100_kernel(const __gri
           ok = wait_all(bar_p_full(t, 1), j & 1, 222 + t);
           if (!ok) break;
           tc_fence_after();
-          if (t == 0) XDIT_TRACE(2, j, 2);
           if (leader) {
             issue_pv_half(t, sv, 1, j == 0);
             if (last_tile) tc_commit(bar_kv_empty(sv));  // V(j) is free once both tiles' PV retire
@@ -552,7 +531,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_sm100_kernel(const __gri
               tc_commit(bar_o_full(t));
             }
           }
-          if (t == 0) XDIT_TRACE(2, j, 6);
         }
         if (!ok) break;
         advance2(sv, pv);
@@ -600,19 +578,12 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_sm100_kernel(const __gri
     auto softmax_tile = [&](auto masked_tag, int j, int v0, int v1) -> bool {
       constexpr bool MASKED = decltype(masked_tag)::value;
       tc_fence_after();
-      XDIT_TRACE(t, j, 0);
       uint32_t s[128];
       XDIT_TMEM_LD32(s, 0, tmem_s + 0);
       XDIT_TMEM_LD32(s, 32, tmem_s + 32);
       XDIT_TMEM_LD32(s, 64, tmem_s + 64);
       XDIT_TMEM_LD32(s, 96, tmem_s + 96);
       tmem_wait_ld();
-      XDIT_TRACE_DEP(t, j, 1, s[0] ^ s[33] ^ s[66] ^ s[127]);
-#ifdef XDIT_DEBUG_DUMP
-      if (a.dbg_s && j == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
-        for (int c = 0; c < 128; ++c) a.dbg_s[(t * 128 + row) * 128 + c] = __uint_as_float(s[c]);
-      }
-#endif
       if constexpr (MASKED) {
 #pragma unroll
         for (int c = 0; c < 128; ++c) {
@@ -634,7 +605,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_sm100_kernel(const __gri
       mx0 = max3(mx0, __uint_as_float(s[124]), __uint_as_float(s[125]));
       mx1 = max3(mx1, __uint_as_float(s[126]), __uint_as_float(s[127]));
       const float mt = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sl2;
-      XDIT_TRACE_DEP(t, j, 2, __float_as_uint(mt));
       if (j == 0) {
         m_run = mt;
       } else {
@@ -696,12 +666,10 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_sm100_kernel(const __gri
         for (int i = 0; i < 16; ++i) pcur[i] = pnext[i];
         if (blk == 3 || blk == 7) {
           const int half = blk >> 2;
-          if (half == 0) XDIT_TRACE_DEP(t, j, 3, pk[0] ^ pk[31]);
           XDIT_TMEM_ST32(pk, 32 * half, tmem_s + 32 * half);
           tmem_wait_st();
           tc_fence_before();
           mbar_arrive(bar_p_full(t, half));
-          if (half == 0) XDIT_TRACE(t, j, 4);
         }
       }
       {
@@ -709,19 +677,18 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_sm100_kernel(const __gri
         f2_unpack(f2_add(f2_add(acc4[0], acc4[1]), f2_add(acc4[2], acc4[3])), a0, a1);
         l_run += a0 + a1;
       }
-      XDIT_TRACE(t, j, 5);
       return true;
     };
     if (tile_on[t]) {
       for (int j = 0; j < n_tiles; ++j) {
-        ok = __all_sync(0xffffffffu, mbar_wait(bar_s_full(t), j & 1, abort_flag, 300 + t));
+        ok = __all_sync(0xffffffffu, mbar_wait(bar_s_full(t), j & 1, abort_flag, a.wait_limit_ns, 300 + t));
         if (!ok) break;
         const int v0 = next_valid(), v1 = next_valid();
         if (v0 < kChunk || v1 < kChunk) softmax_tile(std::true_type{}, j, v0, v1);
         else softmax_tile(std::false_type{}, j, v0, v1);
       }
       // ---------------- epilogue ----------------
-      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_o_full(t), 0, abort_flag, 320 + t));
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_o_full(t), 0, abort_flag, a.wait_limit_ns, 320 + t));
       if (ok) {
         tc_fence_after();
         const int qc = 4 * pair + 2 * t + (row >> 6);
@@ -754,13 +721,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_sm100_kernel(const __gri
           uint32_t o[32];
           XDIT_TMEM_LD32(o, 0, tmem_o + c0);
           tmem_wait_ld();
-#ifdef XDIT_DEBUG_DUMP
-          if (a.dbg_s && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
-            for (int c = 0; c < 32; ++c)
-              a.dbg_s[2 * 128 * 128 + (t * 128 + row) * 128 + c0 + c] = __uint_as_float(o[c]);
-            if (c0 == 0) a.dbg_s[4 * 128 * 128 + t * 128 + row] = l_run;
-          }
-#endif
           if (live) {
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
@@ -806,7 +766,13 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_sm100_kernel(const __gri
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
   }
-  if (threadIdx.x == 0 && *abort_flag > 0 && a.status) atomicCAS(a.status, 0, *abort_flag);
+  if (threadIdx.x == 0 && *abort_flag > 0) {
+    if (a.status) atomicCAS(a.status, 0, *abort_flag);
+    if (a.status_host) {  // host-visible copy, read by the next xdit_attn_fwd call without a synchronise
+      *reinterpret_cast<volatile int32_t*>(a.status_host) = *abort_flag;
+      __threadfence_system();
+    }
+  }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -830,8 +796,62 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
+// Encoded maps are kept in a small direct-mapped cache keyed by everything the encoding depends on
+// (address, extents, strides, dtype): a layer loop that re-uses its buffers, or a graph capture that
+// re-runs the same call, pays for cuTensorMapEncodeTiled once.  A tensor map holds no device state,
+// so an entry stays valid for as long as the same address means the same tensor to the caller.
+struct MapKey {
+  const void* ptr;
+  int64_t st[4];
+  int32_t seg_len, nseg, dtype, B, H, D;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && st[0] == o.st[0] && st[1] == o.st[1] && st[2] == o.st[2] && st[3] == o.st[3] &&
+           seg_len == o.seg_len && nseg == o.nseg && dtype == o.dtype && B == o.B && H == o.H && D == o.D;
+  }
+};
+constexpr int kMapCacheSize = 256;
+struct MapCache {
+  std::mutex mu;
+  bool used[kMapCacheSize] = {};
+  MapKey key[kMapCacheSize];
+  CUtensorMap map[kMapCacheSize];
+};
+MapCache& map_cache() {
+  static MapCache c;
+  return c;
+}
+inline uint32_t map_hash(const MapKey& k) {
+  uint64_t h = (uint64_t)(uintptr_t)k.ptr * 0x9E3779B97F4A7C15ull;
+  for (int i = 0; i < 4; ++i) h = (h ^ (uint64_t)k.st[i]) * 0x100000001B3ull;
+  h = (h ^ (uint64_t)(uint32_t)k.seg_len ^ ((uint64_t)(uint32_t)k.nseg << 32)) * 0x100000001B3ull;
+  h = (h ^ (uint64_t)(uint32_t)k.D ^ ((uint64_t)(uint32_t)k.H << 16) ^ ((uint64_t)(uint32_t)k.B << 40) ^
+       ((uint64_t)(uint32_t)k.dtype << 60)) * 0x100000001B3ull;
+  return (uint32_t)(h >> 40) % kMapCacheSize;
+}
+
+int encode_seq_map_uncached(CUtensorMap* tm, const xdit_seq& s, int dtype, int B, int H, int D);
+
 // 5-D map (d, row, segment, head, batch); a TMA box is 64 elements x 64 rows.
 int encode_seq_map(CUtensorMap* tm, const xdit_seq& s, int dtype, int B, int H, int D) {
+  MapKey k;
+  memset(&k, 0, sizeof(k));
+  k.ptr = s.ptr;
+  k.st[0] = s.stride_row; k.st[1] = s.stride_seg; k.st[2] = s.stride_h; k.st[3] = s.stride_b;
+  k.seg_len = s.seg_len; k.nseg = s.nseg; k.dtype = dtype; k.B = B; k.H = H; k.D = D;
+  const uint32_t slot = map_hash(k);
+  MapCache& c = map_cache();
+  {
+    std::lock_guard<std::mutex> lk(c.mu);
+    if (c.used[slot] && c.key[slot] == k) { *tm = c.map[slot]; return XDIT_OK; }
+  }
+  const int rc = encode_seq_map_uncached(tm, s, dtype, B, H, D);
+  if (rc) return rc;
+  std::lock_guard<std::mutex> lk(c.mu);
+  c.used[slot] = true; c.key[slot] = k; c.map[slot] = *tm;
+  return XDIT_OK;
+}
+
+int encode_seq_map_uncached(CUtensorMap* tm, const xdit_seq& s, int dtype, int B, int H, int D) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) { set_error("cuTensorMapEncodeTiled is not available from the driver"); return XDIT_E_DRIVER; }
   const uint64_t es = 2;
@@ -857,9 +877,9 @@ int encode_seq_map(CUtensorMap* tm, const xdit_seq& s, int dtype, int B, int H, 
   return XDIT_OK;
 }
 
-bool seq_ok(const xdit_seq& s, int B, int H, const char* name) {
+bool seq_ok(const xdit_seq& s, int B, int H, int D, const char* name) {
   if (((uintptr_t)s.ptr) & 15) { set_error("tcgen05 path: %s pointer is not 16-byte aligned", name); return false; }
-  if (s.stride_row < 0 || (s.seg_len > 1 && s.stride_row % 8)) { set_error("tcgen05 path: %s row stride %lld", name, (long long)s.stride_row); return false; }
+  if (s.stride_row < 0 || (s.seg_len > 1 && (s.stride_row % 8 || s.stride_row < D))) { set_error("tcgen05 path: %s row stride %lld", name, (long long)s.stride_row); return false; }
   if (s.nseg > 1 && (s.stride_seg % 8 || s.stride_seg <= 0)) { set_error("tcgen05 path: %s segment stride", name); return false; }
   if (H > 1 && (s.stride_h % 8 || s.stride_h <= 0)) { set_error("tcgen05 path: %s head stride", name); return false; }
   if (B > 1 && (s.stride_b % 8 || s.stride_b <= 0)) { set_error("tcgen05 path: %s batch stride", name); return false; }
@@ -869,14 +889,20 @@ bool seq_ok(const xdit_seq& s, int B, int H, const char* name) {
 template <int SLABS, int NSTAGE, bool BF16>
 int launch_inst(const Sm100Args& a, dim3 grid, cudaStream_t stream) {
   using L = SmemLayout<SLABS, NSTAGE>;
-  static bool configured[16] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 16 || !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(attn_fwd_sm100_kernel<SLABS, NSTAGE, BF16>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
-    if (e != cudaSuccess) return cuda_fail(e, "attn_fwd_sm100 smem attribute");
-    if (dev >= 0 && dev < 16) configured[dev] = true;
+  {
+    // the attribute is per device; set once per device, under a lock (calls may come from several threads)
+    static std::mutex mu;
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    std::lock_guard<std::mutex> lk(mu);
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+      e = cudaFuncSetAttribute(attn_fwd_sm100_kernel<SLABS, NSTAGE, BF16>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
+      if (e != cudaSuccess) return cuda_fail(e, "attn_fwd_sm100 smem attribute");
+      if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
   }
   attn_fwd_sm100_kernel<SLABS, NSTAGE, BF16><<<grid, kThreads, L::kDynamic, stream>>>(a);
   cudaError_t e = cudaGetLastError();
@@ -890,8 +916,8 @@ int attn_sm100_applicable(const xdit_attn_params& p) {
   if (p.dtype != XDIT_BF16 && p.dtype != XDIT_F16) { set_error("tcgen05 path: dtype is not bf16/fp16"); return 0; }
   if (p.D % 8 || p.D < 8 || p.D > 128) { set_error("tcgen05 path: head_dim %d (multiple of 8 up to 128)", p.D); return 0; }
   if (p.causal) { set_error("tcgen05 path: causal masking is served by the CUDA-core kernel"); return 0; }
-  if (!seq_ok(p.q, p.B, p.H, "q") || !seq_ok(p.k, p.B, p.H, "k") || !seq_ok(p.v, p.B, p.H, "v")) return 0;
-  if (p.k2.ptr && (!seq_ok(p.k2, p.B, p.H, "k2") || !seq_ok(p.v2, p.B, p.H, "v2"))) return 0;
+  if (!seq_ok(p.q, p.B, p.H, p.D, "q") || !seq_ok(p.k, p.B, p.H, p.D, "k") || !seq_ok(p.v, p.B, p.H, p.D, "v")) return 0;
+  if (p.k2.ptr && (!seq_ok(p.k2, p.B, p.H, p.D, "k2") || !seq_ok(p.v2, p.B, p.H, p.D, "v2"))) return 0;
   if (!p.acc_out) {
     if (((uintptr_t)p.out) & 15) { set_error("tcgen05 path: out pointer alignment"); return 0; }
     if (p.out_stride_row % 8 || (p.q.nseg > 1 && p.out_stride_seg % 8) || (p.H > 1 && p.out_stride_h % 8) ||
@@ -939,11 +965,9 @@ int launch_attn_sm100(const xdit_attn_params& p, cudaStream_t stream) {
   a.lse = p.lse; a.o_acc = p.o_acc; a.lse_acc = p.lse_acc;
   a.acc_in = p.acc_in; a.acc_out = p.acc_out;
   a.status = p.status;
-#ifdef XDIT_DEBUG_DUMP
-  extern float* g_xdit_dbg_s;
-  a.dbg_s = g_xdit_dbg_s;
-  a.dbg_t = g_xdit_dbg_s ? reinterpret_cast<long long*>(g_xdit_dbg_s + 4 * 128 * 128 + 256) : nullptr;
-#endif
+  a.status_host = p.status_host;
+  a.wait_limit_ns = p.wait_limit_ns ? p.wait_limit_ns : kWaitLimitNs;
+  a.selftest_stall = p.selftest_stall;
   dim3 grid((a.q_chunks + 3) / 4, p.H, p.B);
   const bool bf16 = p.dtype == XDIT_BF16;
   if (p.D <= 64) {
@@ -952,12 +976,6 @@ int launch_attn_sm100(const xdit_attn_params& p, cudaStream_t stream) {
   return bf16 ? launch_inst<2, 5, true>(a, grid, stream) : launch_inst<2, 5, false>(a, grid, stream);
 }
 
-#ifdef XDIT_DEBUG_DUMP
-float* g_xdit_dbg_s = nullptr;
-#endif
 
 }  // namespace xdit
 
-#ifdef XDIT_DEBUG_DUMP
-extern "C" XDIT_API void xdit_debug_set_dump(float* p) { xdit::g_xdit_dbg_s = p; }
-#endif

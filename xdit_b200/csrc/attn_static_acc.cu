@@ -41,15 +41,20 @@ extern "C" XDIT_API int xdit_attn_fwd_static_acc(const struct xdit_attn_params* 
   if (!p) { set_error("xdit_attn_fwd_static_acc: NULL params"); return XDIT_E_NULL; }
   if (p->o_acc || p->lse_acc) {
     set_error("xdit_attn_fwd_static_acc: o_acc/lse_acc must be NULL (the library's own array is used)");
-    return XDIT_E_NULL;
+    return XDIT_E_SHAPE;
   }
   if (!p->acc_in && !p->acc_out) {
     set_error("xdit_attn_fwd_static_acc: neither acc_in nor acc_out is set; call xdit_attn_fwd for a single step");
     return XDIT_E_SHAPE;
   }
-  if (p->B < 1 || p->H < 1 || p->D < 1 || p->q.nseg < 1 || p->q.seg_len < 1) {
-    set_error("xdit_attn_fwd_static_acc: bad shape");
-    return XDIT_E_SHAPE;
+  {
+    // the shared argument check bounds B, H, D and the sequence length before any size is computed;
+    // it wants accumulator pointers for acc_in/acc_out, so it sees a copy that has placeholders
+    xdit_attn_params chk = *p;
+    chk.o_acc = reinterpret_cast<float*>(uintptr_t(256));
+    chk.lse_acc = reinterpret_cast<float*>(uintptr_t(256));
+    const int rc = attn_check(&chk);
+    if (rc) return rc;
   }
   const int64_t rows = (int64_t)p->B * p->H * p->q.nseg * p->q.seg_len;
   // layout inside the array: [rows][D] output accumulator, padded to 64 floats, then [rows] lse

@@ -257,11 +257,13 @@ int xdit_kv_patch_update(const struct xdit_kv_patch_params* p, void* stream) {
   return launch_row_copy(rc, 2, (cudaStream_t)stream);
 }
 
-static int attn_check(const struct xdit_attn_params* p) {
+}  // extern "C"
+namespace xdit {
+int attn_check(const struct xdit_attn_params* p) {
   if (!p) { set_error("xdit_attn_fwd: NULL params"); return XDIT_E_NULL; }
   if (!dtype_size(p->dtype)) { set_error("xdit_attn_fwd: bad dtype %d", p->dtype); return XDIT_E_DTYPE; }
-  if (p->B < 1 || p->H < 1 || p->D < 1 || p->D > 256) {
-    set_error("xdit_attn_fwd: B=%d H=%d D=%d (D must be 1..256)", p->B, p->H, p->D);
+  if (p->B < 1 || p->H < 1 || p->D < 1 || p->D > 256 || p->B > 65535 || p->H > 65535) {
+    set_error("xdit_attn_fwd: B=%d H=%d D=%d (D must be 1..256, B and H at most 65535)", p->B, p->H, p->D);
     return XDIT_E_SHAPE;
   }
   if (!p->q.ptr || !p->k.ptr || !p->v.ptr) { set_error("xdit_attn_fwd: NULL q/k/v"); return XDIT_E_NULL; }
@@ -295,6 +297,9 @@ static int attn_check(const struct xdit_attn_params* p) {
   return XDIT_OK;
 }
 
+}  // namespace xdit
+extern "C" {
+
 int xdit_attn_which(const struct xdit_attn_params* p) {
   int rc = attn_check(p);
   if (rc) return rc;
@@ -305,6 +310,14 @@ int xdit_attn_which(const struct xdit_attn_params* p) {
 int xdit_attn_fwd(const struct xdit_attn_params* p, void* stream) {
   int rc = attn_check(p);
   if (rc) return rc;
+  if (p->status_host) {
+    const int32_t code = *reinterpret_cast<const volatile int32_t*>(p->status_host);
+    if (code != 0) {
+      set_error("xdit_attn_fwd: an earlier launch gave up a bounded wait (code %d); nothing is launched until "
+                "the status words are cleared", code);
+      return XDIT_E_KERNEL_TIMEOUT;
+    }
+  }
   rc = check_device(nullptr);
   if (rc) return rc;
   if (!p->force_generic && attn_sm100_applicable(*p) == 1)

@@ -45,6 +45,8 @@ constexpr int kMaxRowCopyJobs = 8;
 int launch_row_copy(const RowCopyJob* jobs, int njobs, cudaStream_t stream);
 
 // ---- attention kernels ------------------------------------------------------------------------
+// Argument check shared by the attention entry points (bounds B, H, D and the sequence lengths).
+int attn_check(const struct xdit_attn_params* p);
 int launch_attn_generic(const xdit_attn_params& p, cudaStream_t stream);
 // Returns 1 when the tcgen05 kernel accepts p, 0 when it does not (reason in set_error).
 int attn_sm100_applicable(const xdit_attn_params& p);

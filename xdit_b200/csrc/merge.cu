@@ -21,56 +21,74 @@ __device__ inline float logsigmoidf_(float x) {
   return fminf(x, 0.f) - log1pf(__expf(-fabsf(x)));
 }
 
+// One group of LPR lanes (a power of two, at most a warp) owns a row: its lanes stride over the row's
+// vectors, and the row's lse is rewritten only after every lane of the warp has read it
+// (__syncwarp).  A row never spans warps, so no other thread reads lse_acc[r].
 template <typename T, int VEC>
-__global__ void __launch_bounds__(256) merge_kernel(float* __restrict__ o_acc, float* __restrict__ lse_acc,
+__global__ void __launch_bounds__(256) merge_kernel(float* __restrict__ o_acc, float* lse_acc,
                                                    const T* __restrict__ out_b,
                                                    const float* __restrict__ lse_b,
                                                    T* __restrict__ out_final, int64_t rows, int D,
-                                                   int first) {
+                                                   int first, int lpr) {
   const int vpr = D / VEC;
-  const int64_t total = rows * vpr;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-       i += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t r = i / vpr;
-    const int c = (int)(i - r * vpr) * VEC;
-    const float lb = lse_b[r];
-    float w = 0.f, lnew = lb;
-    if (!first) {
-      const float la = lse_acc[r];
-      // both -inf (no keys seen on either side): keep the accumulator
-      if (la == -INFINITY && lb == -INFINITY) { w = 0.f; lnew = la; }
-      else { w = sigmoidf_(lb - la); lnew = la - logsigmoidf_(la - lb); }
-    }
-    float res[VEC];
+  const int lane = threadIdx.x & 31;
+  const int sub = lane & (lpr - 1);        // lane inside its row group
+  const int rows_per_warp = 32 / lpr;
+  const int64_t warp_id = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  const int64_t n_groups = (rows + rows_per_warp - 1) / rows_per_warp;
+  for (int64_t g = warp_id; g < n_groups; g += n_warps) {
+    const int64_t r = g * rows_per_warp + lane / lpr;
+    const bool live = r < rows;
+    float w = 0.f, lnew = 0.f;
+    if (live) {
+      const float lb = lse_b[r];
+      lnew = lb;
+      if (!first) {
+        const float la = lse_acc[r];
+        // both -inf (no keys seen on either side): keep the accumulator
+        if (la == -INFINITY && lb == -INFINITY) { w = 0.f; lnew = la; }
+        else { w = sigmoidf_(lb - la); lnew = la - logsigmoidf_(la - lb); }
+      }
+      for (int v = sub; v < vpr; v += lpr) {
+        const int64_t off = r * D + (int64_t)v * VEC;
+        float res[VEC];
 #pragma unroll
-    for (int k = 0; k < VEC; ++k) {
-      const float ob = to_f<T>(out_b[r * D + c + k]);
-      if (first) res[k] = ob;
-      else { const float oa = o_acc[r * D + c + k]; res[k] = oa - w * (oa - ob); }
-    }
+        for (int k = 0; k < VEC; ++k) {
+          const float ob = to_f<T>(out_b[off + k]);
+          if (first) res[k] = ob;
+          else { const float oa = o_acc[off + k]; res[k] = oa - w * (oa - ob); }
+        }
 #pragma unroll
-    for (int k = 0; k < VEC; ++k) o_acc[r * D + c + k] = res[k];
-    if (out_final) {
+        for (int k = 0; k < VEC; ++k) o_acc[off + k] = res[k];
+        if (out_final) {
 #pragma unroll
-      for (int k = 0; k < VEC; ++k) out_final[r * D + c + k] = from_f<T>(res[k]);
+          for (int k = 0; k < VEC; ++k) out_final[off + k] = from_f<T>(res[k]);
+        }
+      }
     }
-    if (c == 0) lse_acc[r] = lnew;
+    __syncwarp();
+    if (live && sub == 0) lse_acc[r] = lnew;
   }
 }
 
 template <typename T>
 int launch(float* o_acc, float* lse_acc, const void* out_b, const float* lse_b, void* out_final,
            int64_t rows, int D, int first, cudaStream_t stream, int sms) {
-  const int64_t total = rows * (int64_t)(D % 4 == 0 ? D / 4 : D);
-  int64_t blocks = (total + 255) / 256;
+  const int vec = (D % 4 == 0) ? 4 : 1;
+  const int vpr = D / vec;
+  int lpr = 1;
+  while (lpr < vpr && lpr < 32) lpr <<= 1;
+  const int64_t groups = (rows + (32 / lpr) - 1) / (32 / lpr);  // one warp each
+  int64_t blocks = (groups + 7) / 8;
   if (blocks > (int64_t)sms * 16) blocks = (int64_t)sms * 16;
   if (blocks < 1) blocks = 1;
-  if (D % 4 == 0)
+  if (vec == 4)
     merge_kernel<T, 4><<<(int)blocks, 256, 0, stream>>>(o_acc, lse_acc, (const T*)out_b, lse_b,
-                                                         (T*)out_final, rows, D, first);
+                                                         (T*)out_final, rows, D, first, lpr);
   else
     merge_kernel<T, 1><<<(int)blocks, 256, 0, stream>>>(o_acc, lse_acc, (const T*)out_b, lse_b,
-                                                         (T*)out_final, rows, D, first);
+                                                         (T*)out_final, rows, D, first, lpr);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "merge_kernel launch");
   return XDIT_OK;

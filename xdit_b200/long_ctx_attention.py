@@ -98,6 +98,10 @@ def _ring_bhsd(q, k, v, scale, causal, group, R, attn_layer, jk=None, jv=None, f
     from . import ops
 
     B, H, S, D = q.shape
+    if causal and k.shape[2] != S:
+        # the legacy ring only ever masks the diagonal block of equal shards (ring_flash_attn.py:104,113);
+        # for unequal lengths flash-attn's bottom-right alignment would differ from this kernel's top-left
+        raise NotImplementedError("causal ring attention needs equal query and key shard lengths")
     if attn_layer is not None:
         k, v = _usp._update_and_get_kv_cache(k, v, attn_layer)
     out = torch.empty(B, H, S, D, dtype=q.dtype, device=q.device)

@@ -62,27 +62,59 @@ def _seq(t: Optional[torch.Tensor]) -> _capi.Seq:
     return s
 
 
+class _Status:
+    """Per-device pair of status words of the attention kernel: ``dev`` (int32 in device memory, read
+    by every launch) and ``host`` (int32 in pinned, device-mapped host memory, written by a launch
+    only when one of its bounded waits gave up, and read by the C entry point before it launches)."""
+
+    def __init__(self, index: int):
+        self.dev = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", index))
+        self.host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self.index = index
+
+
+def _device_index(device) -> int:
+    device = torch.device(device) if device is not None else torch.device("cuda")
+    return device.index if device.index is not None else torch.cuda.current_device()
+
+
+def _status(device) -> _Status:
+    key = _device_index(device)
+    st = _status_bufs.get(key)
+    if st is None:
+        st = _status_bufs[key] = _Status(key)
+    return st
+
+
 def status_buffer(device) -> torch.Tensor:
     """Per-device int32 word the attention kernel sets when one of its bounded waits gives up."""
-    device = torch.device(device)
-    key = device.index if device.index is not None else torch.cuda.current_device()
-    buf = _status_bufs.get(key)
-    if buf is None:
-        buf = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", key))
-        _status_bufs[key] = buf
-    return buf
+    return _status(device).dev
+
+
+def clear_status(device=None) -> None:
+    """Zero both status words of ``device`` (all devices when None), so that launches run again."""
+    for st in (list(_status_bufs.values()) if device is None else [_status(device)]):
+        st.dev.zero_()
+        st.host.zero_()
 
 
 def check_status(device=None) -> None:
-    """Synchronise and raise if any attention kernel on ``device`` reported a timed-out wait."""
-    keys = list(_status_bufs) if device is None else [torch.device(device).index or 0]
-    for key in keys:
-        buf = _status_bufs.get(key)
-        if buf is None:
+    """Synchronise and raise if any attention kernel on ``device`` (the current device for a bare
+    ``"cuda"``; every device used so far when None) reported a timed-out wait.  The words are cleared
+    before the exception is raised, so that later launches run again.
+
+    Product calls do not need this: a failure also lands in a host-visible word that the next
+    ``xdit_attn_fwd`` call reads without synchronising, and that call raises
+    ``XditError(XDIT_E_KERNEL_TIMEOUT)`` (see :func:`attn_fwd`).  This function is for the end of a
+    run, where no next call follows."""
+    sts = list(_status_bufs.values()) if device is None else [_status_bufs.get(_device_index(device))]
+    for st in sts:
+        if st is None:
             continue
-        code = int(buf.item())
+        code = int(st.dev.item())  # synchronises the device
+        code = code or int(st.host.item())
         if code:
-            buf.zero_()
+            clear_status(torch.device("cuda", st.index))
             raise _capi.XditError(-6, "attention kernel", f"bounded wait gave up (code {code})")
 
 
@@ -109,17 +141,37 @@ def _attn_params(q, k, v, k2, v2, out, lse, o_acc, lse_acc, acc_in, acc_out, cau
     p.acc_in, p.acc_out, p.causal = int(bool(acc_in)), int(bool(acc_out)), int(bool(causal))
     p.softmax_scale = float(scale) if scale else 0.0
     p.force_generic = int(bool(force_generic))
+    st = _status(q.device)
+    p.status = st.dev.data_ptr()
+    p.status_host = st.host.data_ptr()
     return p
+
+
+def _launch_attn(fn, p, q, where):
+    """Call an attention entry point; a timeout reported by an earlier launch surfaces here, and the
+    status words are cleared so that the caller may retry."""
+    with torch.cuda.device(q.device):
+        rc = fn(C.byref(p), _stream(q))
+    if rc == -6:  # XDIT_E_KERNEL_TIMEOUT
+        msg = _capi.load().xdit_last_error_string()
+        torch.cuda.synchronize(q.device)
+        clear_status(q.device)
+        raise _capi.XditError(rc, where, msg.decode() if msg else "")
+    _capi.check(rc, where)
 
 
 def attn_fwd(q, k, v, k2=None, v2=None, *, out=None, lse=None, o_acc=None, lse_acc=None,
              acc_in=False, acc_out=False, causal=False, scale=None, force_generic=False,
-             want_lse=False):
+             want_lse=False, _wait_limit_ns=0, _selftest_stall=False):
     """Dense softmax attention forward (C-ABI ``xdit_attn_fwd``).
 
     Returns ``(out, lse)``.  ``out`` is allocated like ``q`` (contiguous, same dims) unless given;
     ``lse`` ([B,H,Sq] fp32) is produced when ``want_lse`` or when a buffer is passed.  With
     ``acc_out`` the result goes to the fp32 accumulators instead and ``out`` may stay ``None``.
+
+    Raises ``XditError`` (code ``XDIT_E_KERNEL_TIMEOUT``) when an earlier launch on this device gave
+    up one of its bounded waits: that launch's output is invalid, nothing new was launched, and the
+    status words have been cleared so that the caller can retry.
     """
     global launch_count
     _require_cuda(q, k, v, k2, v2, out, lse, o_acc, lse_acc)
@@ -132,9 +184,9 @@ def attn_fwd(q, k, v, k2=None, v2=None, *, out=None, lse=None, o_acc=None, lse_a
     if lse is None and want_lse and not acc_out:
         lse = torch.empty(q.shape[0], q.shape[1], sq, dtype=torch.float32, device=q.device)
     p = _attn_params(q, k, v, k2, v2, out, lse, o_acc, lse_acc, acc_in, acc_out, causal, scale, force_generic)
-    p.status = status_buffer(q.device).data_ptr()
-    with torch.cuda.device(q.device):
-        _capi.check(_capi.load().xdit_attn_fwd(C.byref(p), _stream(q)), "xdit_attn_fwd")
+    p.wait_limit_ns = int(_wait_limit_ns)
+    p.selftest_stall = int(bool(_selftest_stall))
+    _launch_attn(_capi.load().xdit_attn_fwd, p, q, "xdit_attn_fwd")
     launch_count += 1
     return out, lse
 
@@ -143,17 +195,16 @@ def attn_fwd_static_acc(q, k, v, k2=None, v2=None, *, out=None, lse=None, acc_in
                         scale=None, force_generic=False):
     """One ring step through ``xdit_attn_fwd_static_acc``: like :func:`attn_fwd` with ``o_acc`` /
     ``lse_acc``, but the fp32 running accumulators live in a fixed array inside the library, so
-    this wrapper allocates nothing.  ``out`` (and ``lse`` if wanted) must be passed for the last
-    step (``acc_out=False``).  One sequence at a time per device; sizes beyond the built-in
+    this wrapper allocates no device memory apart from the per-device status words (4 bytes of device
+    memory and 4 bytes of pinned host memory, created by the first attention call of any kind on the
+    device).  ``out`` (and ``lse`` if wanted) must be passed for the last step (``acc_out=False``).  One sequence at a time per device; sizes beyond the built-in
     array raise ``XditError``."""
     global launch_count
     _require_cuda(q, k, v, k2, v2, out, lse)
     if not acc_out and out is None:
         raise ValueError("the last step (acc_out=False) needs an output tensor: this entry point allocates nothing")
     p = _attn_params(q, k, v, k2, v2, out, lse, None, None, acc_in, acc_out, False, scale, force_generic)
-    p.status = status_buffer(q.device).data_ptr()
-    with torch.cuda.device(q.device):
-        _capi.check(_capi.load().xdit_attn_fwd_static_acc(C.byref(p), _stream(q)), "xdit_attn_fwd_static_acc")
+    _launch_attn(_capi.load().xdit_attn_fwd_static_acc, p, q, "xdit_attn_fwd_static_acc")
     launch_count += 1
     return out, lse
 

@@ -149,6 +149,11 @@ def select_flash_attn_impl(impl_type=AttnType.FA, stage: str = "fwd-only", attn_
         if softmax_scale is None:
             softmax_scale = 1.0 / math.sqrt(q.size(-1))
         B, S, H, D = q.shape
+        if causal and k.shape[1] != S:
+            # flash-attn aligns a causal mask to the bottom-right corner, the kernel here (like torch
+            # SDPA) to the top-left; the two agree only for equal lengths, which is all the ring uses
+            raise NotImplementedError("causal attention with Sq != Sk: the flash-attn (bottom-right) mask "
+                                      "alignment is not implemented")
         out = torch.empty(B, S, H, D, dtype=q.dtype, device=q.device)
         lse = torch.empty(B, H, S, dtype=torch.float32, device=q.device)
         ops.attn_fwd(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), out=out.transpose(1, 2), lse=lse,
