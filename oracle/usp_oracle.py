@@ -442,6 +442,32 @@ def long_context_attention_bshd(q_shards, k_shards, v_shards, U, R, joint_query=
 # --------------------------------------------------------------------------------------
 # attention prologue of the DiT processors (norm, rotary embedding, head split, pack)
 # --------------------------------------------------------------------------------------
+def round_to_storage(x, kind):
+    """Round float64 values to the nearest ``"bf16"`` (8 significant bits) or ``"f16"`` (11) value, ties to
+    even, returned as float64; ``None`` leaves them alone.  This is where a 16-bit module of the reference
+    rounds: ``torch.nn.RMSNorm`` returns its input's dtype and the processors' rotary helper ends in
+    ``.type_as(hidden_states)`` (``transformer_wan.py:99-100,120``).  Subnormals and overflow are outside
+    the range these activations reach and are not modelled."""
+    if kind is None:
+        return np.asarray(x, dtype=np.float64)
+    x = np.asarray(x, dtype=np.float64)
+    if kind == "f16":
+        return x.astype(np.float16).astype(np.float64)
+    if kind != "bf16":
+        raise ValueError(f"unknown storage type {kind!r}")
+    m, e = np.frexp(x)                      # x = m * 2**e, 0.5 <= |m| < 1
+    return np.ldexp(np.rint(m * 256.0), e - 8)   # np.rint rounds half to even
+
+
+def storage_ulp(x, kind):
+    """Spacing of ``kind`` values in the binade of ``|x|`` (for ``|x|`` below the smallest normal, that of
+    the smallest normal binade)."""
+    bits = {"bf16": 8, "f16": 11}[kind]
+    tiny = {"bf16": 2.0 ** -126, "f16": 2.0 ** -14}[kind]
+    _, e = np.frexp(np.maximum(np.abs(np.asarray(x, dtype=np.float64)), tiny))
+    return np.ldexp(1.0, e - bits)
+
+
 def rms_norm(x, weight, eps, group=None):
     """``torch.nn.RMSNorm`` over the last axis as the processors apply it to the q and k projections:
     ``attn.norm_q(query)`` on ``[B, s, H*D]`` in ``transformer_wan.py:99-100`` (``group=None``: one mean
@@ -474,22 +500,30 @@ def rope_interleaved(x, cos, sin):
     return out
 
 
-def attention_prologue(q, k, v, heads, wq=None, wk=None, eps=1e-6, per_head=False, cos=None, sin=None, U=1):
+def attention_prologue(q, k, v, heads, wq=None, wk=None, eps=1e-6, per_head=False, cos=None, sin=None, U=1,
+                       round_to=None):
     """What a DiT attention processor does between the q/k/v projections and the attention call
     (``transformer_wan.py:97-122,143-147``), followed by the send layout of the Ulysses all-to-all
     (``usp.py:96-108``): norm of q and k, unflatten to heads, rotary embedding of q and k, and for each
     tensor the re-layout ``[B, s, H, D] -> [U][H/U][B][s][D]``.  ``q, k, v`` are ``[B, s, H*D]``;
-    ``cos`` / ``sin`` are ``[s, D]``.  Returns the three send buffers as arrays of that 5-D shape."""
+    ``cos`` / ``sin`` are ``[s, D]``.  Returns the three send buffers as arrays of that 5-D shape.
+
+    ``round_to`` (``"bf16"`` / ``"f16"``) rounds to that storage type at the two places where the
+    reference's 16-bit modules do: the output of the norm and the output of the rotary helper (which
+    multiplies the 16-bit activations with fp32 tables, so the products and their sum are not rounded in
+    between).  With ``round_to`` the result is what a 16-bit implementation is held to, element by
+    element; without it, the exact real-number result."""
     outs = []
     for i, (x, w) in enumerate(((q, wq), (k, wk), (v, None))):
         x = np.asarray(x, dtype=np.float64)
         B, s, HD = x.shape
         D = HD // heads
         if w is not None:
-            x = rms_norm(x, w, eps, group=D if per_head else None)
+            x = round_to_storage(rms_norm(x, w, eps, group=D if per_head else None), round_to)
         x = x.reshape(B, s, heads, D)
         if cos is not None and i < 2:  # q and k only
             x = rope_interleaved(x, np.asarray(cos)[None, :, None, :], np.asarray(sin)[None, :, None, :])
+            x = round_to_storage(x, round_to)
         # [B, s, H, D] -> [U, H/U, B, s, D]
         outs.append(x.transpose(2, 0, 1, 3).reshape(U, heads // U, B, s, D))
     return tuple(outs)

@@ -187,12 +187,19 @@ def _usp_worker(rank, world, port, cases, outdir):
         out = usp.USP(ql, kl, vl, **kwargs)
         gathered = [torch.empty_like(out) for _ in range(P)]
         dist.all_gather(gathered, out.contiguous())
+        # the same call on inputs rounded to bf16 (arithmetic still fp32): what a bf16 implementation is
+        # held to, so that input rounding does not eat into the tolerance
+        rb = lambda t: t.to(torch.bfloat16).to(torch.float32) if torch.is_tensor(t) else t
+        out_b = usp.USP(rb(ql), rb(kl), rb(vl), **{k_: rb(v_) for k_, v_ in kwargs.items()})
+        gathered_b = [torch.empty_like(out_b) for _ in range(P)]
+        dist.all_gather(gathered_b, out_b.contiguous())
         if rank == 0:
             arrays = dict(
                 meta=np.array([U, R, B, H, D, S, Sj, Sk], dtype=np.int64),
                 strategy=np.array(strat or "none"),
                 q=q.numpy(), k=k.numpy(), v=v.numpy(),
                 out=np.stack([g.numpy() for g in gathered]),
+                out_bf16=np.stack([g.numpy() for g in gathered_b]),
             )
             if Sj:
                 arrays.update(jq=jq.numpy(), jk=jk.numpy(), jv=jv.numpy())
@@ -352,14 +359,25 @@ def _usp_kvcache_worker(rank, world, port, outdir):
     state.patch_mode = True
     state.pipeline_patch_idx = 1
     out1 = usp.USP(sh(q1), sh(k1), sh(v1), attn_layer=layer)
+    # the same two steps on inputs rounded to bf16, with a second cache entry
+    rb = lambda t: t.to(torch.bfloat16).to(torch.float32)
+    layer_b = "Lb"
+    cache.get_cache_manager().register_cache_entry(layer_b, "attn", "sequence_parallel_attn_cache")
+    state.patch_mode = False
+    state.pipeline_patch_idx = 0
+    out0b = usp.USP(rb(sh(q0)), rb(sh(k0)), rb(sh(v0)), attn_layer=layer_b)
+    state.patch_mode = True
+    state.pipeline_patch_idx = 1
+    out1b = usp.USP(rb(sh(q1)), rb(sh(k1)), rb(sh(v1)), attn_layer=layer_b)
     outs = []
-    for o in (out0, out1):
+    for o in (out0, out1, out0b, out1b):
         gathered = [torch.empty_like(o) for _ in range(world)]
         dist.all_gather(gathered, o.contiguous())
         outs.append(np.stack([x.numpy() for x in gathered]))
     if rank == 0:
         np.savez_compressed(os.path.join(outdir, "uspkv_u2r1.npz"), q0=q0.numpy(), k0=k0.numpy(), v0=v0.numpy(),
                             q1=q1.numpy(), k1=k1.numpy(), v1=v1.numpy(), out0=outs[0], out1=outs[1],
+                            out0_bf16=outs[2], out1_bf16=outs[3],
                             patches=np.array(patches), patch_idx=np.array(1), U=np.array(U))
     dist.barrier()
     dist.destroy_process_group()
@@ -412,10 +430,24 @@ def _prologue_cases(outdir):
             vv = v.unflatten(2, (H, -1))
             qq, kk = rope(qq, fc, fs), rope(kk, fc, fs)
             outs = [t.transpose(1, 2).contiguous().numpy() for t in (qq, kk, vv)]
+            # the same modules and the same rotary function run in bf16, the way the reference runs them in
+            # a bf16 pipeline (16-bit activations and weights, fp32 cos/sin tables): pins where they round
+            bf = torch.bfloat16
+            import copy
+
+            nq16, nk16 = copy.deepcopy(nq).to(bf), copy.deepcopy(nk).to(bf)
+            q16, k16 = q.to(bf), k.to(bf)
+            if per_head:
+                qq16, kk16 = nq16(q16.unflatten(2, (H, -1))), nk16(k16.unflatten(2, (H, -1)))
+            else:
+                qq16, kk16 = nq16(q16).unflatten(2, (H, -1)), nk16(k16).unflatten(2, (H, -1))
+            qq16, kk16 = rope(qq16, fc, fs), rope(kk16, fc, fs)
+            assert qq16.dtype == bf
+            outs16 = [t.transpose(1, 2).contiguous().float().numpy() for t in (qq16, kk16)]
         np.savez_compressed(os.path.join(outdir, name), q=q.numpy(), k=k.numpy(), v=v.numpy(), cos=cos.numpy(),
                             sin=sin.numpy(), wq=nq.weight.detach().numpy(), wk=nk.weight.detach().numpy(),
                             eps=np.array(eps), heads=np.array(H), per_head=np.array(int(per_head)),
-                            q_out=outs[0], k_out=outs[1], v_out=outs[2])
+                            q_out=outs[0], k_out=outs[1], v_out=outs[2], q_out_bf16=outs16[0], k_out_bf16=outs16[1])
 
 
 def main():

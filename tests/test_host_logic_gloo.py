@@ -20,6 +20,25 @@ def test_world4_matches_reference(mode):
     run(4, golden_files(4), mode, 29730 + ["usp", "legacy", "yunchang"].index(mode))
 
 
+def _need_reference():
+    """The reference's sources for this path: ``oracle/_ref`` (made by ``oracle/make_ref.py``) or a
+    checkout named by ``XDIT_REFERENCE``."""
+    from oracle import make_ref, ref_import
+
+    if ref_import.root() is None and not make_ref.make(quiet=True):
+        pytest.skip("the reference's sources are not here (oracle/make_ref.py makes oracle/_ref from a checkout)")
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_reference_layer_runs_unmodified_on_the_shim(world):
+    """The drop-in claim, exercised: the reference's own ``xFuserLongContextAttention.forward``
+    (``hybrid/attn_layer.py:100-239``) and ``xdit_ring_flash_attn_forward`` (``ring/ring_flash_attn.py:27-148``)
+    run unchanged on top of ``yunchang_compat.install()`` and reproduce the outputs of the reference's
+    ``USP`` (the golden fixtures) -- the identity the reference asserts in ``tests/layers/usp_test.py:211-265``."""
+    _need_reference()
+    run(world, golden_files(world), "ref_layer", 29790 + world)
+
+
 def test_yunchang_shim_serves_the_names_the_reference_imports():
     """xfuser/envs.py:346-352 and the other import sites listed in xdit_b200/yunchang_compat.py."""
     import sys

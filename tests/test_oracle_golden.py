@@ -39,6 +39,27 @@ def test_usp_matches_reference(path):
         np.testing.assert_allclose(outs[g], ref[g], atol=2e-5, rtol=1e-4)
 
 
+def _bf16_round(a):
+    """Round-to-nearest-even to bfloat16, in numpy (what ``tensor.to(torch.bfloat16)`` does)."""
+    u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+    r = ((u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000).astype(np.uint32)
+    return r.view(np.float32)
+
+
+@pytest.mark.parametrize("path", USP_FILES, ids=[os.path.basename(p)[4:-4] for p in USP_FILES])
+def test_usp_on_bf16_rounded_inputs_matches_reference(path):
+    """``out_bf16`` is the reference's result for the inputs rounded to bf16 (arithmetic in fp32): the
+    yardstick of the bf16 GPU tests.  The oracle on the same rounded inputs must reproduce it."""
+    z, U, R, B, H, D, S, Sj, Sk, strat = _load(path)
+    kw = {}
+    if strat:
+        kw = dict(joint_query=_bf16_round(z["jq"]), joint_key=_bf16_round(z["jk"]),
+                  joint_value=_bf16_round(z["jv"]), joint_strategy=strat)
+    outs = O.usp_from_global(_bf16_round(z["q"]), _bf16_round(z["k"]), _bf16_round(z["v"]), U, R, **kw)
+    for g in range(U * R):
+        np.testing.assert_allclose(outs[g], z["out_bf16"][g], atol=2e-5, rtol=1e-4)
+
+
 @pytest.mark.parametrize("path", USP_FILES, ids=[os.path.basename(p)[4:-4] for p in USP_FILES])
 def test_usp_equals_dense_attention(path):
     """Layout-independent property: every rank's rows equal dense attention over all keys."""
@@ -211,3 +232,29 @@ def test_attention_prologue_matches_reference(name):
                               z["cos"], z["sin"], U=2)[0]
     for p in range(2):
         assert np.abs(q2[p].transpose(1, 0, 2, 3) - z["q_out"][:, p * H // 2:(p + 1) * H // 2]).max() < 2e-6
+
+
+@pytest.mark.parametrize("name", ["prologue_wan.npz", "prologue_per_head.npz"])
+def test_attention_prologue_rounding_points_match_the_reference_in_bf16(name):
+    """`q_out_bf16` / `k_out_bf16` were produced by the reference's own norm modules and rotary function
+    run in bf16.  The oracle with ``round_to="bf16"`` (one rounding after norm x weight, one after the
+    rotation) reproduces them bit for bit: that is what pins where a 16-bit implementation may round."""
+    z = np.load(os.path.join(HERE, "golden", name))
+    r = lambda a: O.round_to_storage(a, "bf16")
+    H, per_head = int(z["heads"]), bool(z["per_head"])
+    qs, ks, _ = O.attention_prologue(r(z["q"]), r(z["k"]), r(z["v"]), H, r(z["wq"]), r(z["wk"]), float(z["eps"]),
+                                     per_head, z["cos"], z["sin"], 1, round_to="bf16")
+    np.testing.assert_array_equal(qs[0].transpose(1, 0, 2, 3), z["q_out_bf16"])
+    np.testing.assert_array_equal(ks[0].transpose(1, 0, 2, 3), z["k_out_bf16"])
+
+
+def test_round_to_storage_matches_torch():
+    import torch
+
+    x = np.random.default_rng(0).standard_normal(20000) * np.exp(np.random.default_rng(1).uniform(-8, 8, 20000))
+    x = x.astype(np.float32).astype(np.float64)  # fp32 values: torch rounds a double by way of fp32
+    t = torch.from_numpy(x).float()
+    np.testing.assert_array_equal(O.round_to_storage(x, "bf16"), t.to(torch.bfloat16).double().numpy())
+    np.testing.assert_array_equal(O.round_to_storage(x, "f16"), t.to(torch.float16).double().numpy())
+    assert O.storage_ulp(1.0, "bf16") == 2.0 ** -7 and O.storage_ulp(5.0, "bf16") == 2.0 ** -5
+    assert O.storage_ulp(1.0, "f16") == 2.0 ** -10

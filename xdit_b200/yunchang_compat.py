@@ -18,7 +18,11 @@ the sm_100a kernels, so that the reference's wrappers import and run without the
 ``yunchang.comm.all_to_all``     ``SeqAllToAll4D`` (``attn_layer.py:16``)
 ``yunchang.ring.utils``          ``RingComm, update_out_and_lse`` (``ring_flash_attn.py:11``)
 ``yunchang.ring.ring_flash_attn``  ``RingFlashAttnFunc, ring_flash_attn_backward``
-                                 (``ring_flash_attn.py:12,214``)
+                                 (``ring_flash_attn.py:12,214``), ``ring_flash_attn_forward``
+                                 (``usp_legacy.py:9``)
+``yunchang.ring.ring_pytorch_attn``  ``ring_pytorch_attn_func`` (``usp_legacy.py:10``)
+``yunchang.ring.ring_npu_flash_attn``, ``update_npu_out``  names only (``ring_npu_flash_attn.py:11-13``);
+                                 they raise when called
 ===============================  ==========================================================
 
 None of this is yunchang's code: the semantics are the ones the reference's call sites rely on
@@ -174,19 +178,59 @@ def ring_flash_attn_func(q, k, v, dropout_p=0.0, softmax_scale=None, causal=Fals
                                      deterministic, return_attn_probs, group, attn_type, attn_processor)
 
 
-class RingFlashAttnFunc:
-    """Namespace with the ``apply`` / ``forward`` spelling of the autograd function the reference
-    subclasses (``ring_flash_attn.py:151``).  Forward only."""
+class RingFlashAttnFunc(torch.autograd.Function):
+    """The autograd function the reference subclasses (``ring_flash_attn.py:151``: it overrides
+    ``forward`` / ``backward`` and calls ``.apply`` with its own argument list, which only works on a
+    real ``torch.autograd.Function``).  Applied directly it is plain ring attention.  Forward only."""
 
     @staticmethod
-    def apply(q, k, v, dropout_p, softmax_scale, causal, window_size, alibi_slopes, deterministic,
-              return_softmax, group, attn_type=AttnType.FA, attn_processor=None):
+    def forward(ctx, q, k, v, dropout_p, softmax_scale, causal, window_size, alibi_slopes, deterministic,
+                return_softmax, group, attn_type=AttnType.FA, attn_processor=None):
         return ring_flash_attn_func(q, k, v, dropout_p, softmax_scale, causal, window_size, alibi_slopes,
                                     deterministic, return_softmax, group, attn_type, attn_processor)
+
+    @staticmethod
+    def backward(ctx, *grads):
+        raise NotImplementedError("the attention backward pass is not part of this inference path")
+
+
+def ring_flash_attn_forward(process_group, q, k, v, softmax_scale, dropout_p=0, causal=True, window_size=(-1, -1),
+                            alibi_slopes=None, deterministic=False, attn_type=AttnType.FA, attn_processor=None):
+    """``(out, lse)`` form of the ring function (imported by ``xfuser/model_executor/layers/usp_legacy.py:9``)."""
+    out, lse, _ = xdit_ring_flash_attn_func(q, k, v, dropout_p, softmax_scale, causal, window_size, alibi_slopes,
+                                            deterministic, True, process_group, attn_type, attn_processor)
+    return out, lse
+
+
+def ring_pytorch_attn_func(q, k, v, dropout_p=0.0, softmax_scale=None, causal=False, window_size=(-1, -1),
+                           alibi_slopes=None, deterministic=False, return_attn_probs=False, group=None):
+    """The "pure torch" ring of yunchang (``usp_legacy.py:10,42``): the same ring on the same kernel here."""
+    return xdit_ring_flash_attn_func(q, k, v, dropout_p, softmax_scale, causal, window_size, alibi_slopes,
+                                     deterministic, return_attn_probs, group)
 
 
 def ring_flash_attn_backward(*args, **kwargs):
     raise NotImplementedError("the attention backward pass is not part of this inference path")
+
+
+# Ascend-NPU names that ``xfuser/core/long_ctx_attention/ring/ring_npu_flash_attn.py:11-13,173`` imports
+# whenever a GPU is present; they have to exist for that package to import, and raise when used.
+def update_npu_out(*args, **kwargs):
+    raise NotImplementedError("Ascend NPU attention is not part of this package")
+
+
+class RingNpuFlashAttnFunc(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, *args, **kwargs):
+        raise NotImplementedError("Ascend NPU attention is not part of this package")
+
+    @staticmethod
+    def backward(ctx, *grads):
+        raise NotImplementedError("Ascend NPU attention is not part of this package")
+
+
+def ring_npu_flash_attn_backward(*args, **kwargs):
+    raise NotImplementedError("Ascend NPU attention is not part of this package")
 
 
 class LongContextAttention(torch.nn.Module):
@@ -264,10 +308,15 @@ _TREE = {
     "yunchang.comm": dict(SeqAllToAll4D=SeqAllToAll4D),
     "yunchang.comm.all_to_all": dict(SeqAllToAll4D=SeqAllToAll4D),
     "yunchang.ring": dict(ring_flash_attn_func=ring_flash_attn_func, RingFlashAttnFunc=RingFlashAttnFunc),
-    "yunchang.ring.utils": dict(RingComm=RingComm, update_out_and_lse=update_out_and_lse),
+    "yunchang.ring.utils": dict(RingComm=RingComm, update_out_and_lse=update_out_and_lse,
+                                update_npu_out=update_npu_out),
     "yunchang.ring.ring_flash_attn": dict(RingFlashAttnFunc=RingFlashAttnFunc,
                                           ring_flash_attn_func=ring_flash_attn_func,
+                                          ring_flash_attn_forward=ring_flash_attn_forward,
                                           ring_flash_attn_backward=ring_flash_attn_backward),
+    "yunchang.ring.ring_pytorch_attn": dict(ring_pytorch_attn_func=ring_pytorch_attn_func),
+    "yunchang.ring.ring_npu_flash_attn": dict(RingNpuFlashAttnFunc=RingNpuFlashAttnFunc,
+                                              ring_npu_flash_attn_backward=ring_npu_flash_attn_backward),
 }
 
 
