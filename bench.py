@@ -13,13 +13,20 @@ algorithmic TFLOP/s (4*Sq*Sk*H*D per call) over all GPUs with inputs resident in
 is the same metric through ``xdit_b200.USP`` with the step's inputs in pinned host memory and
 the results read back, copies inside the timed region.
 
-N > 1 is launched by ``torch.distributed.run`` (one rank per GPU, NCCL); the sequence is sharded
-over N ranks (strong scaling) with Ulysses degree N, which is the fastest split behind NVSwitch
-(measured at 8 GPUs on the 75.6K workload: U8 7755, U4xR2 7438, U2xR4 6872, R8 6046 TFLOP/s);
-``--sp ULYSSESxRING`` selects another split, e.g. ``--sp 2x4`` for Ulysses 2 x ring 4, the split the Wan2.1 workload is usually quoted with.
+Before anything is timed, every rank runs one ``USP`` call of each workload and compares sampled
+rows of its result with the oracle's dense attention over the regenerated global tensors; the line
+carries ``parity`` and the process exits non-zero when a row is outside max-abs 2e-2 / cosine
+0.9999.
 
-``--impl reference`` times the CPU restatement of the reference's algorithm (the oracle) on the
-host cores of rank 0, on a bounded sample (a subset of heads) of the same workload.
+N > 1 is launched by ``torch.distributed.run`` (one rank per GPU, NCCL); the sequence is sharded
+over N ranks (strong scaling) with Ulysses degree N, which is the fastest split behind NVSwitch;
+``--sp ULYSSESxRING`` selects another split, e.g. ``--sp 2x4`` for Ulysses 2 x ring 4, the split the
+Wan2.1 workload is usually quoted with.  Ring splits are also measured (and checked) as legs under
+``extra``.
+
+``--impl reference`` times the reference's own ``USP()`` (its unmodified Python, taken from
+``oracle/_ref``) on the host cores of rank 0, on a bounded sample of the same workload; without
+those sources it times the oracle's restatement instead and says so (``kind``).
 """
 from __future__ import annotations
 
@@ -35,12 +42,17 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 WORKLOADS = {
-    # name: layers, heads, head_dim, tokens, {n_gpus: (ulysses, ring)}
+    # name: layers, heads, head_dim, tokens
     "flux": dict(desc="Flux.1-dev 1024x1024 MMDiT self-attention: 57 layers x (24 heads x 128, 512 text + 4096 image tokens)",
-                 layers=57, sets=57, H=24, D=128, S=4608, degrees={1: (1, 1), 2: (2, 1), 4: (4, 1), 8: (8, 1)}),
+                 layers=57, sets=57, H=24, D=128, S=4608),
     "wan": dict(desc="Wan2.1-14B 81f 720x1280 self-attention: 40 layers x (40 heads x 128, 75,600 tokens)",
-                layers=40, sets=2, H=40, D=128, S=75600, degrees={1: (1, 1), 2: (2, 1), 4: (4, 1), 8: (8, 1)}),
+                layers=40, sets=2, H=40, D=128, S=75600),
+    # legs reported under `extra`
+    "hunyuan": dict(desc="HunyuanVideo 129f 720p self-attention: 24 heads x 128, 256 text + 118,800 image tokens, "
+                         "text sharded with the image",
+                    layers=60, sets=1, H=24, D=128, S=119056),
 }
+TOL_MAX_ABS, TOL_COS = 2e-2, 0.9999
 
 
 def peaks():
@@ -137,21 +149,126 @@ class ClockSampler:
                 "samples": len(s)}
 
 
+def bind_to_gpu_numa_node(index: int) -> bool:
+    """Run this rank on the cores next to its GPU (the affinity NVML reports), so that the pinned host
+    buffers of the end-to-end leg are first touched on that memory node.  A setting of this process
+    only; returns whether it could be applied."""
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(index)
+        words = ((os.cpu_count() or 64) + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(h, words)
+        cpus = {64 * i + b for i, word in enumerate(mask) for b in range(64) if (word >> b) & 1}
+        cpus &= os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            return True
+    except Exception:
+        pass
+    return False
+
+
 def flops_per_call(w):
     return 4.0 * w["S"] * w["S"] * w["H"] * w["D"]
 
 
 # --------------------------------------------------------------------------------------------
-# reference arm: the CPU restatement of the reference algorithm on the host cores
+# reference arm and CPU baseline: the reference's own USP() on the host cores
 # --------------------------------------------------------------------------------------------
-def run_reference(args, w, name):
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
-        return
-    import torch
+def _reference_usp_callable():
+    """(callable(q, k, v) -> out, kind).  The reference's own ``USP`` at sequence-parallel degree 1
+    (``usp.py:316-323``: its ``SDPA`` back-end body, no collectives) when its sources are under
+    ``oracle/_ref``; otherwise the oracle's restatement of that call."""
+    from oracle import ref_import
 
+    if ref_import.root() is not None:
+        usp, backend, _cache, _rts = ref_import.import_usp()
+        ref_import.configure_usp(usp, backend, 1, 1, 0, None, None)
+        return usp.USP, "reference"
     from oracle import usp_oracle as O
 
+    return O.attention_dense_torch_cpu, "port"
+
+
+def _config1_gloo_worker(rank, world, port, threads, q):
+    """Two gloo ranks running the reference's ``USP`` on the Flux-shaped fp32 joint case: Ulysses 2,
+    24 heads x 128, 4096 image tokens sharded + 512 text tokens replicated (joint, rear), N(0,1) from
+    seed 0.  One warm-up and five timed calls, each followed by a barrier; rank 0 reports the median."""
+    import torch
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(threads)
+    from oracle import ref_import
+
+    usp, backend, _cache, _rts = ref_import.import_usp()
+    pg = dist.new_group(list(range(world)), backend="gloo")
+    ref_import.configure_usp(usp, backend, world, 1, rank, pg, None)
+    g = torch.Generator().manual_seed(0)
+    B, H, D, S, Sj = 1, 24, 128, 4096, 512
+    qg, kg, vg = (torch.randn(B, H, S, D, generator=g) for _ in range(3))
+    jq, jk, jv = (torch.randn(B, H, Sj, D, generator=g) for _ in range(3))
+    sh = lambda t: t.chunk(world, dim=2)[rank].contiguous()
+    ql, kl, vl = sh(qg), sh(kg), sh(vg)
+    ts = []
+    for it in range(6):
+        dist.barrier()
+        t0 = time.perf_counter()
+        out = usp.USP(ql, kl, vl, joint_query=jq, joint_key=jk, joint_value=jv, joint_strategy="rear")
+        dist.barrier()
+        if it:
+            ts.append(time.perf_counter() - t0)
+    if rank == 0:
+        ts.sort()
+        # parity of what was timed: rank 0's rows against dense attention over all keys
+        import torch.nn.functional as F
+
+        dense = F.scaled_dot_product_attention(torch.cat([ql, jq], 2), torch.cat([kg, jk], 2), torch.cat([vg, jv], 2))
+        q.put({"median_s": ts[len(ts) // 2], "calls": len(ts), "max_abs_vs_dense": float((out - dense).abs().max())})
+    dist.destroy_process_group()
+
+
+def reference_config1_gloo(cores):
+    """The reference's ``USP`` under 2 gloo ranks on the host cores (threads = cores / 2 each)."""
+    from oracle import ref_import
+
+    if ref_import.root() is None:
+        return {"unavailable": "the reference's sources are not under oracle/_ref"}
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.SimpleQueue()
+    threads = max(1, cores // 2)
+    port = 29400 + os.getpid() % 500
+    procs = [ctx.Process(target=_config1_gloo_worker, args=(r, 2, port, threads, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+    for p in procs:
+        if p.is_alive():
+            p.terminate()
+    if q.empty() or any(p.exitcode != 0 for p in procs):
+        return {"unavailable": "the 2-rank gloo run did not finish"}
+    r = q.get()
+    fl = 4.0 * (4096 + 512) * (4096 + 512) * 24 * 128  # text rows counted once
+    return {"tflops": fl / r["median_s"] / 1e12, "median_ms": r["median_s"] * 1e3, "calls": r["calls"],
+            "ranks": 2, "threads_per_rank": threads, "cores": cores, "dtype": "f32",
+            "max_abs_vs_dense": r["max_abs_vs_dense"],
+            "what": "reference USP(), Ulysses 2 over gloo, 24 x 128, 4096 image + 512 joint text tokens (rear), "
+                    "1 warm-up + 5 timed calls, median"}
+
+
+def host_sample(w, budget_s, steps, warmup):
+    """Time the reference's CPU path on a bounded sample (a number of heads of one layer) of workload
+    ``w``; returns (TFLOP/s, ms per step, description, kind, cores)."""
+    import torch
+
+    fn, kind = _reference_usp_callable()
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     S, D = w["S"], w["D"]
@@ -162,31 +279,39 @@ def run_reference(args, w, name):
 
     def one(qkv):
         t0 = time.perf_counter()
-        O.attention_dense_torch_cpu(*qkv)
+        fn(*qkv)
         return time.perf_counter() - t0
 
-    # size the per-step sample (a number of heads of one layer) so that the whole run stays near 90 s
     t_head = one(make(1))
-    budget = 90.0 / max(1, args.steps + args.warmup)
-    heads = int(max(1, min(w["H"], budget / max(t_head, 1e-3))))
-    qkv = make(heads)  # one input set, larger than any CPU cache (heads x 75,600 x 128 fp32 x 3)
-    for _ in range(args.warmup):
+    per_step = budget_s / max(1, steps + warmup)
+    heads = int(max(1, min(w["H"], per_step / max(t_head, 1e-3))))
+    qkv = make(heads)  # one input set, larger than any CPU cache (heads x S x 128 fp32 x 3)
+    for _ in range(warmup):
         one(qkv)
     total = 0.0
-    for _ in range(args.steps):
+    for _ in range(steps):
         total += one(qkv)
     fl = 4.0 * S * S * heads * D
-    val = fl * args.steps / total / 1e12
-    sample = (f"{heads} of {w['H']} heads of one layer, {S} tokens, fp32 torch CPU SDPA "
-              f"(the reference's SDPA back-end body) on {cores} threads, per step")
+    name = "the reference's USP() at sequence-parallel degree 1 (its SDPA back-end)" if kind == "reference" \
+        else "the oracle's restatement of the reference's SDPA back-end"
+    sample = (f"{heads} of {w['H']} heads of one layer, {S} tokens, fp32, {name} on {cores} threads, per step")
+    return fl * steps / total / 1e12, total / steps * 1e3, sample, kind, cores
+
+
+def run_reference(args, w, name):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    val, ms, sample, kind, cores = host_sample(w, 90.0, args.steps, args.warmup)
     line = {
         "impl": "reference", "metric": "usp_attn_tflops", "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": total / args.steps * 1e3,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": name, "desc": w["desc"]},
-        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
+        "extra": {"flux_joint_fp32_ulysses2_gloo": reference_config1_gloo(cores)},
     }
     print(json.dumps(line), flush=True)
 
@@ -194,24 +319,70 @@ def run_reference(args, w, name):
 # --------------------------------------------------------------------------------------------
 # our arm
 # --------------------------------------------------------------------------------------------
-def make_layer_inputs(torch, w, P, rank, layers, device, pinned=False):
-    """``layers`` distinct input sets of local shards [1, H, S/P, D] bf16 (a step cycles through
-    them layer by layer)."""
+def global_head(torch, device, set_idx, tensor_idx, head, S, D, rows=None):
+    """N(0,1) rows of one head of a *global* tensor, drawn on the device from a seed that depends only
+    on (input set, tensor, head): every rank can regenerate any head, which is what lets each rank
+    check its own output rows against dense attention over all keys.  bf16 [S, D] (or the row range)."""
+    g = torch.Generator(device=device)
+    g.manual_seed(1000003 * (set_idx + 1) + 10007 * tensor_idx + head)
+    t = torch.randn(S, D, generator=g, dtype=torch.float32, device=device).to(torch.bfloat16)
+    return t if rows is None else t[rows[0]:rows[1]]
+
+
+def make_layer_inputs(torch, w, P, rank, sets, device, pinned=False):
+    """``sets`` distinct input sets of local shards [1, H, S/P, D] bf16 (a step cycles through them
+    layer by layer); rank r holds rows [r*S/P, (r+1)*S/P) of the global tensors."""
     S, H, D = w["S"], w["H"], w["D"]
     s = S // P
     out = []
-    gg = torch.Generator(device=device)
-    for layer in range(layers):
+    for si in range(sets):
         qkv = []
         for i in range(3):
-            # N(0,1) drawn on the device from a seed per (layer, tensor, rank); host sets are copies
-            gg.manual_seed(1000003 * (layer + 1) + 1009 * i + rank)
-            t = torch.randn(1, H, s, D, generator=gg, dtype=torch.float32, device=device).to(torch.bfloat16)
+            t = torch.empty(1, H, s, D, dtype=torch.bfloat16, device=device)
+            for h in range(H):
+                t[0, h].copy_(global_head(torch, device, si, i, h, S, D, (rank * s, (rank + 1) * s)))
             if pinned:
                 t = t.cpu().pin_memory()
             qkv.append(t)
         out.append(tuple(qkv))
     return out
+
+
+def parity_check(torch, dist, out, w, P, rank, device, multi, set_idx=0):
+    """Sampled rows (first / middle / last 64 of this rank's shard, first and last head) of ``out``
+    [1,H,s,D] against the oracle's dense attention in float64 over the regenerated global K and V."""
+    import numpy as np
+
+    from oracle import usp_oracle as O
+
+    S, H, D = w["S"], w["H"], w["D"]
+    s = S // P
+    n = min(64, s)
+    rows = sorted(set(list(range(n)) + list(range(s // 2 - n // 2, s // 2 - n // 2 + n)) + list(range(s - n, s))))
+    heads = sorted({0, H - 1})
+    idx = torch.tensor(rows, device=device)
+    f64 = lambda t: t.float().cpu().double().numpy()
+    max_abs, cos_min = 0.0, 1.0
+    for h in heads:
+        q = global_head(torch, device, set_idx, 0, h, S, D, (rank * s, (rank + 1) * s))[idx]
+        k = global_head(torch, device, set_idx, 1, h, S, D)
+        v = global_head(torch, device, set_idx, 2, h, S, D)
+        want, _ = O.attention_dense(f64(q)[None, None], f64(k)[None, None], f64(v)[None, None])
+        got = f64(out[0, h][idx])
+        want = want[0, 0]
+        max_abs = max(max_abs, float(np.abs(got - want).max()))
+        cos_min = min(cos_min, float((got * want).sum() / (np.linalg.norm(got) * np.linalg.norm(want) + 1e-30)))
+    finite = bool(torch.isfinite(out.float()).all().item())
+    nrows = len(rows) * len(heads)
+    if multi:
+        t = torch.tensor([max_abs, -cos_min, 0.0 if finite else 1.0], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        max_abs, cos_min, finite = float(t[0]), -float(t[1]), float(t[2]) == 0.0
+        nrows *= dist.get_world_size()
+    ok = finite and max_abs <= TOL_MAX_ABS and cos_min >= TOL_COS
+    return {"max_abs": max_abs, "cos": cos_min, "rows": nrows, "heads": heads, "finite": finite, "ok": ok,
+            "against": "oracle dense attention (float64) over the regenerated global q/k/v",
+            "tolerance": {"max_abs": TOL_MAX_ABS, "cos": TOL_COS}}
 
 
 def timed_region(torch, dist, fn, steps, warmup, device, multi):
@@ -237,18 +408,21 @@ def timed_region(torch, dist, fn, steps, warmup, device, multi):
     return ms
 
 
-def run_workload(torch, dist, xdit_b200, ops, name, w, args, device, rank, world, layers, with_e2e):
-    U, R = w["degrees"][world]
-    if getattr(args, "sp", None):
-        U, R = (int(x) for x in args.sp.lower().split("x"))
-        assert U * R == world, "--sp UxR must multiply to the number of GPUs"
+def run_workload(torch, dist, xdit_b200, ops, name, w, args, device, rank, world, layers, with_e2e, U, R):
     xdit_b200.init_sequence_parallel(U, R)
     P = U * R
     S = w["S"]
-    assert S % P == 0
+    assert P == world and S % P == 0
     nsets = max(1, min(layers, w["sets"]))
     inputs = make_layer_inputs(torch, w, P, rank, nsets, device)
     multi = world > 1
+
+    # correctness first: one call, sampled rows against the oracle
+    out = xdit_b200.USP(*inputs[0])
+    torch.cuda.synchronize(device)
+    ops.check_status()
+    parity = parity_check(torch, dist, out, w, P, rank, device, multi)
+    del out
 
     def step_eager():
         for layer in range(layers):
@@ -283,24 +457,26 @@ def run_workload(torch, dist, xdit_b200, ops, name, w, args, device, rank, world
         "launches": launches,
         "clocks": sampler.summary(),
         "U": U, "R": R, "layers": layers, "cuda_graph": graphed, "sets": nsets, "steps": args.steps,
+        "parity": parity,
     }
     if with_e2e:
         host = make_layer_inputs(torch, w, P, rank, nsets, device, pinned=True)
         s = S // P
         host_out = [torch.empty(1, w["H"], s, w["D"], dtype=torch.bfloat16).pin_memory() for _ in range(nsets)]
 
-        # The way a serving loop stages a layer's tensors: two device slots, the next layer's q/k/v
+        # The way a serving loop stages a layer's tensors: three device slots, the next layers' q/k/v
         # copied in on one side stream while this layer's USP call runs, the result copied out on
         # another.  Every byte still crosses PCIe inside the timed region, every step.
+        NSLOT = 3
         cur = torch.cuda.current_stream(device)
         s_in, s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
         slots = [[torch.empty(1, w["H"], s, w["D"], dtype=torch.bfloat16, device=device) for _ in range(3)]
-                 for _ in range(2)]
-        ev_in = [torch.cuda.Event() for _ in range(2)]
-        ev_done = [torch.cuda.Event() for _ in range(2)]
+                 for _ in range(NSLOT)]
+        ev_in = [torch.cuda.Event() for _ in range(NSLOT)]
+        ev_done = [torch.cuda.Event() for _ in range(NSLOT)]
 
         def stage(layer):
-            slot = layer & 1
+            slot = layer % NSLOT
             s_in.wait_event(ev_done[slot])  # the call that last read this slot has finished
             with torch.cuda.stream(s_in):
                 for dst, src in zip(slots[slot], host[layer % nsets]):
@@ -310,11 +486,12 @@ def run_workload(torch, dist, xdit_b200, ops, name, w, args, device, rank, world
         def step_e2e():
             for e in ev_done:
                 e.record(cur)
-            stage(0)
+            for layer in range(min(NSLOT - 1, layers)):
+                stage(layer)
             for layer in range(layers):
-                slot = layer & 1
-                if layer + 1 < layers:
-                    stage(layer + 1)
+                slot = layer % NSLOT
+                if layer + NSLOT - 1 < layers:
+                    stage(layer + NSLOT - 1)
                 cur.wait_event(ev_in[slot])
                 out = xdit_b200.USP(*slots[slot])
                 ev_done[slot].record(cur)
@@ -324,17 +501,54 @@ def run_workload(torch, dist, xdit_b200, ops, name, w, args, device, rank, world
                 out.record_stream(s_out)
             cur.wait_stream(s_out)  # the step ends when its last result is in host memory
 
-        e2e_steps = max(1, min(args.steps, 2 if w["S"] > 20000 else 5))
+        e2e_steps = max(1, min(args.steps, 5))
         ms_e = timed_region(torch, dist, step_e2e, e2e_steps, 1, device, multi)
+        ops.check_status()
         bytes_in = 3 * layers * w["H"] * s * w["D"] * 2
         bytes_out = layers * w["H"] * s * w["D"] * 2
         res["e2e"] = {"value": fl_step * e2e_steps / (ms_e * 1e-3) / 1e12, "unit": "TFLOP/s",
                       "h2d_bytes_per_step": bytes_in, "d2h_bytes_per_step": bytes_out,
-                      "ms_per_step": ms_e / e2e_steps, "steps": e2e_steps}
-        del host, host_out
+                      "ms_per_step": ms_e / e2e_steps, "steps": e2e_steps, "warmup": 1,
+                      "host_gbs_per_rank": (bytes_in + bytes_out) / (ms_e / e2e_steps * 1e-3) / 1e9}
+        del host, host_out, slots
     del inputs
     torch.cuda.empty_cache()
     return res
+
+
+def leg(torch, dist, xdit_b200, ops, name, w, args, device, rank, world, layers, U, R, tf_peak, steps=3):
+    """A secondary measurement (another workload or another split): same timing rules, same parity
+    check, a few layers or steps, no end-to-end part.  Never takes the main line down."""
+    try:
+        a2 = argparse.Namespace(steps=max(1, min(args.steps, steps)), warmup=3, graph=args.graph)
+        r = run_workload(torch, dist, xdit_b200, ops, name, w, a2, device, rank, world, layers, False, U, R)
+        P = U * R
+        out = {
+            "desc": w["desc"], "layers_timed": layers, "ulysses": U, "ring": R, "cuda_graph": r["cuda_graph"],
+            "tflops_all_gpus": r["tflops"], "tflops_per_gpu": r["tflops"] / world,
+            "ms_per_layer_call": r["ms_per_step"] / layers,
+            "frac_of_measured_bf16_burst_peak": r["tflops"] / world / tf_peak,
+            "parity": r["parity"],
+        }
+        if P > 1:
+            out["nvlink"] = nvlink_bytes(w, U, R)
+        return out, r["parity"]["ok"]
+    except Exception as e:  # noqa: BLE001
+        import traceback
+
+        return {"error": repr(e)[:300], "trace": traceback.format_exc()[-600:]}, False
+
+
+def nvlink_bytes(w, U, R):
+    """Algorithmic bytes one rank sends per attention call: the Ulysses exchanges move (U-1)/U of q, k,
+    v and of the output; the ring sends the local K/V shard R-1 times.  ``floor_ms`` is that volume at
+    the nominal 900 GB/s per direction."""
+    P = U * R
+    n = w["H"] * (w["S"] // P) * w["D"] * 2  # bytes of one local tensor
+    uly = 4 * n * (U - 1) / U if U > 1 else 0.0
+    ring = (R - 1) * 2 * (w["H"] // U) * (w["S"] // R) * w["D"] * 2 if R > 1 else 0.0
+    return {"ulysses_bytes_per_call": uly, "ring_bytes_per_call": ring,
+            "floor_ms_at_900GBs": (uly + ring) / 900e9 * 1e3}
 
 
 def hbm_kernels(torch, ops, device, hbm_peak, peak_kind):
@@ -413,6 +627,163 @@ def hbm_kernels(torch, ops, device, hbm_peak, peak_kind):
     return res
 
 
+def pixart_leg(torch, xdit_b200, ops, device, tf_peak):
+    """PixArt-Sigma 2048x2048 with PipeFusion in its steady state, as one GPU of the pipeline sees it:
+    16 heads x 72, a patch of 2048 fresh tokens attends to the layer's 16,384-token K/V buffer of which
+    7/8 is stale; every call first writes the patch's fresh K/V rows into the buffer
+    (``USP(..., attn_layer=...)`` -> stale-KV manager -> ``xdit_kv_patch_update``), then attends.
+    7 layers of a pipeline stage x 8 patches per timed pass."""
+    import numpy as np
+
+    from oracle import usp_oracle as O
+
+    H, D, S, NP, LAYERS = 16, 72, 16384, 8, 7
+    n = S // NP
+    xdit_b200.init_sequence_parallel(1, 1)
+    rs = xdit_b200.initialize_runtime_state()
+    rs.set_patches([n] * NP)
+    mgr = xdit_b200.get_cache_manager()
+    bf = torch.bfloat16
+    g = torch.Generator(device=device)
+    g.manual_seed(72)
+    mk = lambda rows: torch.randn(1, rows, H, D, generator=g, device=device, dtype=torch.float32).to(bf).transpose(1, 2)
+    layers = [f"pixart_layer_{i}" for i in range(LAYERS)]
+    full = {}
+    rs.set_patched_mode(False)
+    for name in layers:  # warm-up step: full sequence, fills the buffers
+        mgr.register_cache_entry(name, "attn", "naive_cache")
+        q, k, v = mk(S), mk(S), mk(S)
+        full[name] = (k, v)
+        xdit_b200.USP(q, k, v, attn_layer=name)
+    fresh = {name: [(mk(n), mk(n), mk(n)) for _ in range(NP)] for name in layers}
+    rs.set_patched_mode(True)
+
+    def one_pass():
+        for p in range(NP):
+            rs.pipeline_patch_idx = p
+            for name in layers:
+                q, k, v = fresh[name][p]
+                xdit_b200.USP(q, k, v, attn_layer=name)
+
+    # parity of one steady-state call: patch 3 of layer 0 against dense attention over the buffer it
+    # must see (warm-up rows, rows of patch 3 replaced by the fresh ones)
+    name, p = layers[0], 3
+    rs.pipeline_patch_idx = p
+    q, k, v = fresh[name][p]
+    out = xdit_b200.USP(q, k, v, attn_layer=name)
+    torch.cuda.synchronize(device)
+    kk, vv = full[name][0].clone(), full[name][1].clone()
+    kk[:, :, p * n:(p + 1) * n], vv[:, :, p * n:(p + 1) * n] = k, v
+    f64 = lambda t: t.float().cpu().double().numpy()
+    rows = slice(0, 96)
+    want, _ = O.attention_dense(f64(q[:, :2, rows]), f64(kk[:, :2]), f64(vv[:, :2]))
+    got = f64(out[:, :2, rows])
+    max_abs = float(np.abs(got - want).max())
+    cos = float((got * want).sum() / (np.linalg.norm(got) * np.linalg.norm(want)))
+    ok = max_abs <= TOL_MAX_ABS and cos >= TOL_COS
+    for _ in range(3):
+        one_pass()
+    torch.cuda.synchronize(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 5
+    e0.record()
+    for _ in range(reps):
+        one_pass()
+    e1.record()
+    torch.cuda.synchronize(device)
+    ops.check_status()
+    ms = e0.elapsed_time(e1) / reps
+    calls = NP * LAYERS
+    fl = 4.0 * n * S * H * D * calls
+    rs.set_patched_mode(False)
+    rs.set_patches([])
+    return {"desc": "PixArt-Sigma 2048x2048 PipeFusion steady state on one GPU: 16 heads x 72, 2048 fresh of 16,384 "
+                    "tokens per call, stale-KV patch update + attention, 7 layers x 8 patches per pass",
+            "calls_per_pass": calls, "ms_per_call": ms / calls, "tflops_per_gpu": fl / (ms * 1e-3) / 1e12,
+            "frac_of_measured_bf16_burst_peak": fl / (ms * 1e-3) / 1e12 / tf_peak,
+            "l2": "7 layers x (2 x 37.7 MB of K/V buffers + fresh rows) = 0.6 GB cycled, larger than L2",
+            "parity": {"max_abs": max_abs, "cos": cos, "rows": 192, "ok": ok,
+                       "against": "oracle dense attention over the patched K/V buffer"}}, ok
+
+
+def gpu_backends(torch, device, ours_ms, tf_peak):
+    """The library kernels the reference would dispatch to on this GPU, timed as black boxes next to
+    this package's kernel: one Flux layer and one Wan layer, local tensors on one GPU, CUDA events.
+    Called through the reference's own registered back-end functions
+    (``xfuser/core/distributed/attention_backend.py:504-516, 550-566, 887-918, 644-673``) when its sources are
+    under ``oracle/_ref``, else through the same aten / flash_attn calls those functions make."""
+    shapes = {"flux": (24, 4608, 128, 5), "wan": (40, 75600, 128, 2)}
+    calls = {}
+    source = "aten / flash_attn calls as the reference's back-end functions make them"
+    try:
+        from oracle import ref_import
+
+        if ref_import.root() is not None:
+            _usp, backend, _c, _r = ref_import.import_usp()
+            T = backend.AttentionBackendType
+            reg = backend.ATTENTION_FUNCTION_REGISTRY
+            for key, member in (("cudnn", T.CUDNN), ("sdpa_flash", T.SDPA_FLASH), ("flash", T.FLASH),
+                                ("flash_4", T.FLASH_4)):
+                if member in reg:
+                    calls[key] = (lambda q, k, v, f=reg[member]: f(q, k, v, 0.0, False))
+            source = "the reference's own registered back-end functions (oracle/_ref)"
+    except Exception:  # noqa: BLE001
+        calls = {}
+    aten = torch.ops.aten
+    calls.setdefault("cudnn", lambda q, k, v: aten._scaled_dot_product_cudnn_attention(
+        q, k, v, attn_bias=None, compute_log_sumexp=True, dropout_p=0.0, is_causal=False))
+    calls.setdefault("sdpa_flash", lambda q, k, v: aten._scaled_dot_product_flash_attention(
+        q, k, v, dropout_p=0.0, is_causal=False))
+
+    def _fa2(q, k, v):
+        from flash_attn import flash_attn_func
+
+        return flash_attn_func(q.permute(0, 2, 1, 3), k.permute(0, 2, 1, 3), v.permute(0, 2, 1, 3), dropout_p=0.0,
+                               causal=False, return_attn_probs=True)
+
+    def _fa4(q, k, v):
+        from flash_attn.cute.interface import flash_attn_func as fa4
+
+        return fa4(q.permute(0, 2, 1, 3).contiguous(), k.permute(0, 2, 1, 3).contiguous(),
+                   v.permute(0, 2, 1, 3).contiguous(), causal=False)
+
+    calls.setdefault("flash", _fa2)
+    calls.setdefault("flash_4", _fa4)
+    res = {"source": source}
+    for wname, (H, S, D, reps) in shapes.items():
+        g = torch.Generator(device=device)
+        g.manual_seed(5)
+        q, k, v = (torch.randn(1, H, S, D, generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+                   for _ in range(3))
+        fl = 4.0 * S * S * H * D
+        row = {"ours_ms": ours_ms.get(wname), "ours_tflops": fl / (ours_ms[wname] * 1e-3) / 1e12
+               if ours_ms.get(wname) else None}
+        for key, fn in calls.items():
+            try:
+                for _ in range(2):
+                    fn(q, k, v)
+                torch.cuda.synchronize(device)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(reps):
+                    fn(q, k, v)
+                e1.record()
+                torch.cuda.synchronize(device)
+                ms = e0.elapsed_time(e1) / reps
+                row[key] = {"ms": ms, "tflops": fl / (ms * 1e-3) / 1e12,
+                            "ours_over_it": (ms / ours_ms[wname]) if ours_ms.get(wname) else None}
+            except Exception as e:  # noqa: BLE001
+                row[key] = {"unavailable": "unavailable on this box: " + repr(e)[:160]}
+                try:
+                    torch.cuda.synchronize(device)
+                except Exception:  # noqa: BLE001
+                    pass
+        res[wname] = row
+        del q, k, v
+        torch.cuda.empty_cache()
+    return res
+
+
 # --------------------------------------------------------------------------------------------
 # DiT step latency on random-init stand-ins of the named architectures (plain torch bf16 for
 # everything but attention; no checkpoint or diffusers is available here)
@@ -420,18 +791,21 @@ def hbm_kernels(torch, ops, device, hbm_peak, peak_kind):
 def dit_step_latency(torch, dist, xdit_b200, kind, device, rank, world, reps=5, fused_prologue=True):
     """One transformer forward (= one denoising step) of a Flux.1-dev-shaped MMDiT or a
     Wan2.1-14B-shaped video DiT: QKV/out projections, MLPs and norms in torch bf16 with N(0, 0.02)
-    weights, the sequence sharded over the ranks.  Self-attention from the projections on: with
+    weights, the sequence sharded over the ranks (Ulysses degree = ranks), and the model-exit sequence
+    gather that hands every rank the full output.  Self-attention from the projections on: with
     ``fused_prologue`` through ``xdit_b200.prologue.attention_from_projections`` (q/k RMS-norm, rotary
-    embedding, head split and pack in one kernel), otherwise q/k RMS-norm and rotary embedding in
-    torch and ``xdit_b200.USP``, the way the reference's processors are written.  Text cross-attention
-    through ``xdit_b200.attention``.  Returns milliseconds (median)."""
+    embedding, head split and pack in one kernel; the head merge feeds the output projection without a
+    re-layout copy), otherwise q/k RMS-norm and rotary embedding in torch and ``xdit_b200.USP``, the way
+    the reference's processors are written.  Text cross-attention through ``xdit_b200.attention``.
+    Returns milliseconds (median)."""
     import torch.nn.functional as F
 
+    from xdit_b200.model_boundary import gather_sequence
     from xdit_b200.prologue import attention_from_projections
 
     bf = torch.bfloat16
     w = WORKLOADS[kind]
-    U, R = w["degrees"][world]
+    U, R = world, 1
     xdit_b200.init_sequence_parallel(U, R)
     P = U * R
     H, D, S = w["H"], w["D"], w["S"]
@@ -458,24 +832,24 @@ def dit_step_latency(torch, dist, xdit_b200, kind, device, rank, world, reps=5, 
         out[..., 1::2] = x1 * rotary[1][..., 1::2] + x2 * rotary[0][..., 0::2]
         return out
 
-    def attn(q, k, v):  # [B, s, H, D] views of the projections -> [B, s, H*D]
+    def attn(q, k, v, w_out):  # [B, s, H, D] views of the projections -> output projection applied
         if fused_prologue:
             return attention_from_projections(q.reshape(1, s, hid), k.reshape(1, s, hid), v.reshape(1, s, hid), H,
                                               norm_q_weight=wq, norm_k_weight=wk, eps=1e-6, norm_per_head=per_head,
-                                              rotary_emb=rotary)
+                                              rotary_emb=rotary, out_proj_weight=w_out)
         if per_head:
             q, k = F.rms_norm(q, (D,), wq, 1e-6), F.rms_norm(k, (D,), wk, 1e-6)
         else:
             q = F.rms_norm(q.reshape(1, s, hid), (hid,), wq, 1e-6).view(1, s, H, D)
             k = F.rms_norm(k.reshape(1, s, hid), (hid,), wk, 1e-6).view(1, s, H, D)
         o = xdit_b200.USP(rope(q).transpose(1, 2), rope(k).transpose(1, 2), v.transpose(1, 2))
-        return o.transpose(1, 2).reshape(1, s, hid)
+        return F.linear(o.transpose(1, 2).reshape(1, s, hid), w_out)
 
     x = torch.randn(1, s, hid, device=device, generator=g).to(bf)
     if kind == "flux":
         mlp = 4 * hid
         dbl = [dict(qkv=lin(hid, 3 * hid), proj=lin(hid, hid), up=lin(hid, mlp), down=lin(mlp, hid)) for _ in range(19)]
-        sgl = [dict(l1=lin(hid, 3 * hid + mlp), l2=lin(hid + mlp, hid)) for _ in range(38)]
+        sgl = [dict(l1=lin(hid, 3 * hid + mlp), l2a=lin(hid, hid), l2m=lin(mlp, hid)) for _ in range(38)]
 
         def forward(x):
             # text and image tokens form one sharded sequence; a double block differs from a single
@@ -484,13 +858,14 @@ def dit_step_latency(torch, dist, xdit_b200, kind, device, rank, world, reps=5, 
             for b in dbl:
                 h_ = F.layer_norm(x, (hid,))
                 q, k, v = F.linear(h_, b["qkv"]).view(1, s, 3, H, D).unbind(2)
-                x = x + F.linear(attn(q, k, v), b["proj"])
+                x = x + attn(q, k, v, b["proj"])
                 x = x + F.linear(F.gelu(F.linear(F.layer_norm(x, (hid,)), b["up"]), approximate="tanh"), b["down"])
             for b in sgl:
                 h_ = F.linear(F.layer_norm(x, (hid,)), b["l1"])
                 q, k, v = h_[..., : 3 * hid].view(1, s, 3, H, D).unbind(2)
-                x = x + F.linear(torch.cat([attn(q, k, v), F.gelu(h_[..., 3 * hid:], approximate="tanh")], -1), b["l2"])
-            return x
+                # the single block's output projection over cat(attention, MLP) is the sum of its two halves
+                x = x + attn(q, k, v, b["l2a"]) + F.linear(F.gelu(h_[..., 3 * hid:], approximate="tanh"), b["l2m"])
+            return gather_sequence(x, dim=1)
     else:
         ffn, txt_len, txt_dim = 13824, 512, 4096
         ctx = torch.randn(1, txt_len, txt_dim, device=device, generator=g).to(bf)
@@ -502,17 +877,17 @@ def dit_step_latency(torch, dist, xdit_b200, kind, device, rank, world, reps=5, 
             for b in blocks:
                 h_ = F.layer_norm(x, (hid,))
                 q, k, v = (F.linear(h_, b[n]).view(1, s, H, D) for n in ("q", "k", "v"))
-                x = x + F.linear(attn(q, k, v), b["o"])
+                x = x + attn(q, k, v, b["o"])
                 h_ = F.layer_norm(x, (hid,))
                 cq = F.linear(h_, b["cq"]).view(1, s, H, D).transpose(1, 2)
                 ck = F.linear(ctx, b["ck"]).view(1, txt_len, H, D).transpose(1, 2)
                 cv = F.linear(ctx, b["cv"]).view(1, txt_len, H, D).transpose(1, 2)
                 x = x + F.linear(xdit_b200.attention(cq, ck, cv).transpose(1, 2).reshape(1, s, hid), b["co"])
                 x = x + F.linear(F.gelu(F.linear(F.layer_norm(x, (hid,)), b["up"]), approximate="tanh"), b["down"])
-            return x
+            return gather_sequence(x, dim=1)
 
     with torch.no_grad():
-        for _ in range(2):
+        for _ in range(2 if kind == "flux" else 1):
             forward(x)
         times = []
         for _ in range(reps):
@@ -530,35 +905,16 @@ def dit_step_latency(torch, dist, xdit_b200, kind, device, rank, world, reps=5, 
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     return {"ms_per_step": ms, "ulysses": U, "ring": R, "reps": reps,
-            "what": "one forward of a random-init stand-in (torch bf16 linears/norms/MLPs + xdit_b200 attention; "
-                    + ("q/k norm + rotary embedding + head split fused with the pack" if fused_prologue
+            "what": "one forward of a random-init stand-in (torch bf16 linears/norms/MLPs + xdit_b200 attention + "
+                    "the model-exit sequence gather; "
+                    + ("q/k norm + rotary embedding + head split fused with the pack, head merge fed to the output "
+                       "projection without a copy" if fused_prologue
                        else "q/k norm and rotary embedding in torch, as the reference's processors do") + ")"}
 
 
 def cpu_baseline(w):
-    import torch
-
-    from oracle import usp_oracle as O
-
-    cores = os.cpu_count() or 1
-    torch.set_num_threads(cores)
-    S, D, heads = w["S"], w["D"], w["H"]
-    if S > 20000:
-        S, heads = 9450, 8  # a shard-sized sample: the full score matrix is too much for a bounded host run
-    g = torch.Generator().manual_seed(0)
-    total, fl, reps = 0.0, 0.0, 0
-    q, k, v = (torch.randn(1, heads, S, D, generator=g) for _ in range(3))
-    O.attention_dense_torch_cpu(q, k, v)  # warm-up
-    t_end = time.perf_counter() + 12.0
-    while time.perf_counter() < t_end and reps < 20:
-        t0 = time.perf_counter()
-        O.attention_dense_torch_cpu(q, k, v)
-        total += time.perf_counter() - t0
-        fl += 4.0 * S * S * heads * D
-        reps += 1
-    return {"value": fl / total / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
-            "sample": f"{reps} x one layer call ({heads} heads, {S} tokens, fp32), torch CPU SDPA as the "
-                      f"reference's SDPA back-end calls it, {cores} threads"}
+    val, ms, sample, kind, cores = host_sample(w, 15.0, 3, 1)
+    return {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": kind, "sample": sample}
 
 
 def main():
@@ -566,11 +922,11 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default="wan", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="wan", choices=["flux", "wan"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--no-extra", action="store_true", help="skip the secondary workload and the CPU baseline")
+    ap.add_argument("--no-extra", action="store_true", help="skip the secondary workloads, legs and the CPU baseline")
     ap.add_argument("--layers", type=int, default=0, help="time only this many layers per step (profiling aid)")
-    ap.add_argument("--dit", default="flux", choices=["none", "flux", "wan", "both"],
+    ap.add_argument("--dit", default="both", choices=["none", "flux", "wan", "both"],
                     help="also time one DiT forward of a random-init stand-in of this architecture (extra.dit_step)")
     ap.add_argument("--sp", default=None, help="override the sequence-parallel degrees of the main workload: ULYSSESxRING, e.g. 2x4")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end (host buffers) leg")
@@ -595,6 +951,8 @@ def main():
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the kernels have no CPU fallback")
+    cpus_before = os.sched_getaffinity(0)
+    numa_bound = bind_to_gpu_numa_node(local)
     device = torch.device("cuda", local)
     torch.cuda.set_device(device)
     if world > 1:
@@ -613,42 +971,66 @@ def main():
     tf_peak, tf_sustained, hbm_peak, peak_kind = peaks()
     if args.layers > 0:
         w = dict(w, layers=min(args.layers, w["layers"]))
+    U, R = world, 1
+    if args.sp:
+        U, R = (int(x) for x in args.sp.lower().split("x"))
+        assert U * R == world, "--sp UxR must multiply to the number of GPUs"
     main_res = run_workload(torch, dist, xdit_b200, ops, name, w, args, device, rank, world, w["layers"],
-                            not args.no_e2e)
+                            not args.no_e2e, U, R)
+    all_ok = main_res["parity"]["ok"]
     extra = {}
     if not args.no_extra:
         other = "wan" if name == "flux" else "flux"
         wo = WORKLOADS[other]
-        a2 = argparse.Namespace(steps=max(1, min(args.steps, 3)), warmup=3, graph=args.graph, sp=None)
         layers = 4 if other == "wan" else wo["layers"]
-        try:
-            r2 = run_workload(torch, dist, xdit_b200, ops, other, wo, a2, device, rank, world, layers, False)
-            extra[other] = {
-                "desc": wo["desc"], "layers_timed": layers, "ulysses": r2["U"], "ring": r2["R"],
-                "cuda_graph": r2["cuda_graph"],
-                "tflops_all_gpus": r2["tflops"], "tflops_per_gpu": r2["tflops"] / world,
-                "ms_per_layer_call": r2["ms_per_step"] / layers,
-                "frac_of_measured_bf16_burst_peak": r2["tflops"] / world / tf_peak,
-            }
-        except Exception as e:  # the secondary workload must not take the main line down
-            extra[other] = {"error": repr(e)[:200]}
+        extra[other], ok = leg(torch, dist, xdit_b200, ops, other, wo, args, device, rank, world, layers, world, 1,
+                               tf_peak)
+        all_ok &= ok
+        # ring legs: the K/V rotation over NCCL with the merge in the kernel epilogue, checked the same way
+        if world > 1:
+            splits = [(1, world)] + ([(2, 4)] if world == 8 else []) + ([(2, 2)] if world == 4 else [])
+            for (u, r) in splits:
+                extra[f"wan_ring_u{u}r{r}"], ok = leg(torch, dist, xdit_b200, ops, "wan", WORKLOADS["wan"], args,
+                                                      device, rank, world, 4, u, r, tf_peak, steps=2)
+                all_ok &= ok
+        # the ring-dominant long-context case (119,056 tokens); ring degree = ranks, one GPU runs it dense
+        wh = WORKLOADS["hunyuan"]
+        if wh["S"] % world == 0:
+            extra["hunyuan_ring"], ok = leg(torch, dist, xdit_b200, ops, "hunyuan", wh, args, device, rank, world,
+                                            2, 1, world, tf_peak, steps=2)
+            all_ok &= ok
         if world == 1:
             try:
+                extra["pixart_pipefusion_steady"], ok = pixart_leg(torch, xdit_b200, ops, device, tf_peak)
+                all_ok &= ok
+            except Exception as e:  # noqa: BLE001
+                extra["pixart_pipefusion_steady"] = {"error": repr(e)[:300]}
+            try:
                 extra["hbm_kernels"] = hbm_kernels(torch, ops, device, hbm_peak, peak_kind)
-            except Exception as e:
+            except Exception as e:  # noqa: BLE001
                 extra["hbm_kernels"] = {"error": repr(e)[:200]}
+            try:
+                ours_ms = {name: main_res["ms_per_step"] / w["layers"]}
+                if "ms_per_layer_call" in extra.get(other, {}):
+                    ours_ms[other] = extra[other]["ms_per_layer_call"]
+                extra["gpu_backends"] = gpu_backends(torch, device, ours_ms, tf_peak)
+            except Exception as e:  # noqa: BLE001
+                extra["gpu_backends"] = {"error": repr(e)[:200]}
         if args.dit != "none":
             extra["dit_step"] = {}
             for kind in (("flux", "wan") if args.dit == "both" else (args.dit,)):
                 try:
-                    reps = 5 if kind == "flux" else 3
+                    reps = 5 if kind == "flux" else 2
                     r_f = dit_step_latency(torch, dist, xdit_b200, kind, device, rank, world, reps=reps)
-                    r_t = dit_step_latency(torch, dist, xdit_b200, kind, device, rank, world, reps=reps,
-                                           fused_prologue=False)
-                    r_f["ms_per_step_torch_prologue"] = r_t["ms_per_step"]
+                    if kind == "flux":
+                        r_t = dit_step_latency(torch, dist, xdit_b200, kind, device, rank, world, reps=reps,
+                                               fused_prologue=False)
+                        r_f["ms_per_step_torch_prologue"] = r_t["ms_per_step"]
                     extra["dit_step"][kind] = r_f
-                except Exception as e:
-                    extra["dit_step"][kind] = {"error": repr(e)[:200]}
+                except Exception as e:  # noqa: BLE001
+                    import traceback
+
+                    extra["dit_step"][kind] = {"error": repr(e)[:200], "trace": traceback.format_exc()[-500:]}
                 torch.cuda.empty_cache()
 
     if rank == 0:
@@ -667,20 +1049,27 @@ def main():
                 "head_dim": w["D"], "global_batch": 1,
                 "l2": f"inputs larger than L2: {main_res['sets']} distinct q/k/v sets cycled layer by layer "
                       f"({main_res['sets'] * 3 * w['H'] * w['S'] * w['D'] * 2 / 1e9:.1f} GB over all ranks)",
+                "host_numa_bound": numa_bound,
             },
             "tflops_per_gpu": per_gpu_tf,
+            "parity": dict(main_res["parity"], all_legs_ok=bool(all_ok)),
             "roofline": roofline(w, main_res, per_gpu_tf, kernel_ms, world, tf_peak, tf_sustained, peak_kind),
             "e2e": main_res.get("e2e"),
             "clocks": main_res["clocks"],
             "gpu_launches": main_res["launches"],
             "extra": extra,
         }
+        if world > 1:
+            line["nvlink"] = nvlink_bytes(w, main_res["U"], main_res["R"])
         if world == 1 and not args.no_extra:
+            os.sched_setaffinity(0, cpus_before)  # the host baseline gets every core again
             line["cpu_baseline"] = cpu_baseline(w)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if not all_ok:
+        raise SystemExit("parity check failed: a sampled row is outside max-abs 2e-2 / cosine 0.9999 (see `parity`)")
 
 
 if __name__ == "__main__":

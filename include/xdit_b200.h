@@ -189,6 +189,26 @@ XDIT_API int xdit_ulysses_unpack_out(const void* recv, void* dst, int32_t dtype,
 XDIT_API int xdit_ulysses_unpack_in(const void* recv, void* dst, int32_t dtype, int32_t B, int32_t Hl,
                            int32_t s, int32_t D, int32_t U, void* stream);
 
+/* Sequence sharding at the model boundary.
+ *
+ * xdit_seq_shard_pad: the rows of src [B,S,C] (element strides stride_b, stride_row; C contiguous)
+ * that sequence-parallel rank `rank` of W owns after S has been zero-padded up to a multiple of W:
+ * dst [B, s, C] contiguous with s = ceil(S/W), rows at or past S written as zeros.  One pass over the
+ * local rows only.  Replaces: torch.cat([x, zeros]) + torch.chunk(...)[rank]
+ * (xfuser/model_executor/models/transformers/transformer_wan.py:219-234 _chunk_and_pad_sequence;
+ * transformer_flux.py:279-284, 307-309).
+ *
+ * xdit_seq_gather_unpad: recv [W][B][s][C] (what all_gather_into_tensor leaves) -> dst [B][keep][C],
+ * keep = W*s - padding rows, i.e. the gathered sequence with the padding dropped, in one pass.
+ * Replaces: reshape([W,...]).movedim(0, dim).reshape(...) of GroupCoordinator.all_gather
+ * (xfuser/core/distributed/group_coordinator.py:243-262) and the narrow / slice that drops the
+ * padding (transformer_wan.py:236-239 _gather_and_unpad; transformer_flux.py:333-336). */
+XDIT_API int xdit_seq_shard_pad(const void* src, int64_t stride_b, int64_t stride_row, void* dst,
+                                int32_t dtype, int32_t B, int32_t S, int32_t C, int32_t W, int32_t rank,
+                                void* stream);
+XDIT_API int xdit_seq_gather_unpad(const void* recv, void* dst, int32_t dtype, int32_t W, int32_t B,
+                                   int32_t s, int32_t C, int32_t keep, void* stream);
+
 /* PipeFusion stale-KV patch update: overwrite rows [row_start, row_start + nseg*n) of the
  * persistent K and V caches (attention layout, strides given) with fresh rows.  The fresh rows
  * come as `nseg` segments of `n` rows (one segment per Ulysses source rank; nseg = 1 without

@@ -527,3 +527,28 @@ def attention_prologue(q, k, v, heads, wq=None, wk=None, eps=1e-6, per_head=Fals
         # [B, s, H, D] -> [U, H/U, B, s, D]
         outs.append(x.transpose(2, 0, 1, 3).reshape(U, heads // U, B, s, D))
     return tuple(outs)
+
+
+# --------------------------------------------------------------------------------------------
+# model boundary: zero-pad + shard at entry, gather + unpad at exit
+# --------------------------------------------------------------------------------------------
+def pad_and_shard_sequence(x, world, dim=1):
+    """Every rank's chunk of ``x`` along ``dim`` after zero-padding that axis up to a multiple of ``world``
+    (``transformer_wan.py:219-234``: ``torch.cat([x, zeros])`` then ``torch.chunk(x, world, dim)[rank]``).
+    Returns ``(list of chunks, pad_amount)``."""
+    x = np.asarray(x)
+    n = x.shape[dim]
+    pad = (world - n % world) % world
+    if pad:
+        shape = list(x.shape)
+        shape[dim] = pad
+        x = np.concatenate([x, np.zeros(shape, dtype=x.dtype)], axis=dim)
+    return np.split(x, world, axis=dim), pad
+
+
+def gather_and_unpad(chunks, pad, dim=-2):
+    """``GroupCoordinator.all_gather(x, dim)`` (``group_coordinator.py:221-262``: rank order along ``dim``)
+    followed by dropping the last ``pad`` rows (``transformer_wan.py:236-239``)."""
+    x = np.concatenate([np.asarray(c) for c in chunks], axis=dim)
+    n = x.shape[dim]
+    return np.take(x, np.arange(n - pad), axis=dim)

@@ -20,13 +20,20 @@ def _np(x):
     return x.detach().to(torch.float64).numpy()
 
 
+FAST_FP32 = False  # large shapes: torch's fp32 CPU attention instead of the float64 numpy one
+
+
 def attn_fwd(q, k, v, k2=None, v2=None, *, out=None, lse=None, o_acc=None, lse_acc=None, acc_in=False,
-             acc_out=False, causal=False, scale=None, force_generic=False, want_lse=False):
+             acc_out=False, causal=False, scale=None, force_generic=False, want_lse=False, **_):
     q4, k4, v4 = _flat4(q), _flat4(k), _flat4(v)
     if k2 is not None:
         k4 = torch.cat([k4, k2], dim=2)
         v4 = torch.cat([v4, v2], dim=2)
-    o, l = O.attention_dense(_np(q4), _np(k4), _np(v4), scale=scale, causal=causal)
+    if FAST_FP32 and not causal and scale is None:
+        o, l = torch.ops.aten._scaled_dot_product_flash_attention_for_cpu(q4.float(), k4.float(), v4.float())
+        o, l = o.double().numpy(), l.double().numpy()
+    else:
+        o, l = O.attention_dense(_np(q4), _np(k4), _np(v4), scale=scale, causal=causal)
     if acc_in:
         o, l = O.merge_out_lse(_np(o_acc), _np(lse_acc), o, l)
     if acc_out:
@@ -100,12 +107,22 @@ def qk_norm_rope_pack(q, k, v, heads, dst_q, dst_k, dst_v, peer_strides, U=1, *,
             dst[p * stride:p * stride + blk].copy_(torch.from_numpy(o[p].reshape(-1)).to(dst.dtype))
 
 
+def seq_shard_pad(x, rank, world):
+    chunks, _ = O.pad_and_shard_sequence(x.detach().numpy(), world, dim=1)
+    return torch.from_numpy(np.ascontiguousarray(chunks[rank])).to(x.dtype)
+
+
+def seq_gather_unpad(recv, B, s, Cn, world, keep):
+    chunks = [recv[w].detach().numpy() for w in range(world)]
+    return torch.from_numpy(np.ascontiguousarray(O.gather_and_unpad(chunks, world * s - keep, dim=1))).to(recv.dtype)
+
+
 def install(monkeypatch_or_none=None):
     """Replace the CUDA wrappers of ``xdit_b200.ops`` with the CPU stand-ins above."""
     import xdit_b200.ops as ops
 
     names = ["attn_fwd", "ulysses_pack", "ulysses_unpack_in", "ulysses_pack_out", "ulysses_unpack_out",
-             "kv_patch_update", "merge_out_lse", "qk_norm_rope_pack"]
+             "kv_patch_update", "merge_out_lse", "qk_norm_rope_pack", "seq_shard_pad", "seq_gather_unpad"]
     for n in names:
         if monkeypatch_or_none is not None:
             monkeypatch_or_none.setattr(ops, n, globals()[n])

@@ -450,10 +450,71 @@ def _prologue_cases(outdir):
                             q_out=outs[0], k_out=outs[1], v_out=outs[2], q_out_bf16=outs16[0], k_out_bf16=outs16[1])
 
 
+def _reference_wan_methods(names):
+    """Methods of the reference's Wan wrapper taken from the file's syntax tree (importing the module
+    would need diffusers): ``xfuser/model_executor/models/transformers/transformer_wan.py:219-239``."""
+    import ast
+
+    path = os.path.join(REF, "xfuser", "model_executor", "models", "transformers", "transformer_wan.py")
+    src = open(path).read()
+    found = {}
+    for node in ast.walk(ast.parse(src)):
+        if isinstance(node, ast.FunctionDef) and node.name in names:
+            found[node.name] = ast.get_source_segment(src, node)
+    assert set(found) == set(names), found.keys()
+    return found
+
+
+def _boundary_worker(rank, world, port, outdir):
+    """Model-boundary sharding as the reference does it: ``_chunk_and_pad_sequence`` at entry,
+    ``_gather_and_unpad`` at exit on top of the real ``GroupCoordinator.all_gather`` (gloo ranks)."""
+    import functools
+    import textwrap
+    import types as _types
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import_reference()
+    gc = importlib.import_module("xfuser.core.distributed.group_coordinator")
+    fake_group = _types.SimpleNamespace(world_size=world, device_group=dist.group.WORLD)
+    fake_group.all_gather = functools.partial(gc.GroupCoordinator.all_gather, fake_group)
+    srcs = _reference_wan_methods(["_chunk_and_pad_sequence", "_gather_and_unpad"])
+    ns = {"torch": torch, "get_sp_group": lambda: fake_group}
+    for body in srcs.values():
+        exec(textwrap.dedent(body), ns)
+    chunk_pad, gather_unpad = ns["_chunk_and_pad_sequence"], ns["_gather_and_unpad"]
+    g = torch.Generator().manual_seed(99)
+    rec = {}
+    for name, shape, dim in (("a", (2, 10, 6), 1), ("b", (1, 13, 8), -2), ("c", (2, 3, 9, 4), 2), ("d", (1, 8, 16), 1)):
+        x = torch.randn(*shape, generator=g)
+        n = shape[dim]
+        pad = (world - n % world) % world
+        local = chunk_pad(None, x, rank, world, pad, dim)
+        back = gather_unpad(None, local.contiguous() * 1.0, pad, dim)
+        locs = [torch.empty_like(local.contiguous()) for _ in range(world)]
+        dist.all_gather(locs, local.contiguous())
+        if rank == 0:
+            rec[f"{name}_x"] = x.numpy()
+            rec[f"{name}_dim"] = np.array(dim)
+            rec[f"{name}_pad"] = np.array(pad)
+            rec[f"{name}_chunks"] = np.stack([t.numpy() for t in locs])
+            rec[f"{name}_gathered"] = back.contiguous().numpy()
+    if rank == 0:
+        rec["world"] = np.array(world)
+        rec["names"] = np.array(["a", "b", "c", "d"])
+        np.savez_compressed(os.path.join(outdir, f"boundary_w{world}.npz"), **rec)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def main():
     outdir = HERE
     if "--prologue-only" in sys.argv:
         _prologue_cases(outdir)
+        return
+    if "--boundary-only" in sys.argv:
+        mp.spawn(_boundary_worker, args=(4, 29631, outdir), nprocs=4, join=True)
         return
     port = 29611
     for world in (1, 2, 4):
@@ -466,6 +527,7 @@ def main():
     _layout_cases(outdir)
     _cache_cases(outdir)
     _prologue_cases(outdir)
+    mp.spawn(_boundary_worker, args=(4, port + 1, outdir), nprocs=4, join=True)
     print("golden fixtures written to", outdir)
 
 

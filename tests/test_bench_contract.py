@@ -36,6 +36,22 @@ def test_workloads_match_the_named_configs():
     assert (wan["H"], wan["D"], wan["S"], wan["layers"]) == (40, 128, 75600, 40)
     assert abs(b.flops_per_call(flux) - 2.609e11) / 2.609e11 < 1e-3
     assert abs(b.flops_per_call(wan) - 1.1705e14) / 1.1705e14 < 1e-3
-    for w in (flux, wan):
-        for n, (u, r) in w["degrees"].items():
-            assert u * r == n and w["H"] % u == 0 and w["S"] % (u * r) == 0
+    hun = b.WORKLOADS["hunyuan"]
+    assert (hun["H"], hun["D"], hun["S"]) == (24, 128, 118800 + 256)
+    for w in (flux, wan, hun):
+        for n in (1, 2, 4, 8):  # Ulysses degree = ranks for flux/wan, ring degree = ranks for hunyuan
+            assert w["S"] % n == 0 and (w is hun or w["H"] % n == 0)
+    assert (b.TOL_MAX_ABS, b.TOL_COS) == (2e-2, 0.9999)
+
+
+def test_nvlink_bytes_per_call():
+    b = _bench()
+    wan = b.WORKLOADS["wan"]
+    # Ulysses 2 x ring 4: q,k,v and the output each move half of a local tensor; the ring sends the
+    # K/V shard of 20 heads x 18,900 rows three times
+    r = b.nvlink_bytes(wan, 2, 4)
+    local = 40 * 9450 * 128 * 2
+    assert r["ulysses_bytes_per_call"] == 4 * local / 2
+    assert r["ring_bytes_per_call"] == 3 * 2 * 20 * 18900 * 128 * 2
+    assert abs(r["ring_bytes_per_call"] - 580.6e6) / 580.6e6 < 1e-3
+    assert b.nvlink_bytes(wan, 1, 1)["floor_ms_at_900GBs"] == 0.0

@@ -7,7 +7,7 @@ import torch
 
 import os
 
-from tests.usp_worker import HERE, golden_files, run, run_kv, run_prologue
+from tests.usp_worker import HERE, golden_files, run, run_flux_joint, run_kv, run_prologue
 
 pytestmark = pytest.mark.gpu
 
@@ -68,3 +68,11 @@ def test_attention_from_projections_two_gpus(U, R):
     the all-to-all send buffer, ring 2 hands [B,H,s,D] tensors to the ring path."""
     _need(2)
     run_prologue(2, U, R, 29780 + R, backend="nccl", dtype_name="bfloat16", tol=2e-2)
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 5e-5), ("bfloat16", 2e-2)])
+def test_flux_joint_case_at_full_size_two_gpus(dtype, tol):
+    """Ulysses 2 over NCCL at the full Flux-shaped joint case: 24 heads x 128, 4096 image + 512 joint text
+    tokens (rear), seed 0; fp32 (CUDA-core kernel) and bf16 (tcgen05 kernel) against the float64 oracle."""
+    _need(2)
+    run_flux_joint(2, 29762, backend="nccl", dtype_name=dtype, tol=tol)

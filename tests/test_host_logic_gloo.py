@@ -7,7 +7,7 @@ import pytest
 
 import os
 
-from tests.usp_worker import HERE, golden_files, run, run_kv, run_prologue
+from tests.usp_worker import HERE, golden_files, run, run_flux_joint, run_kv, run_prologue
 
 
 @pytest.mark.parametrize("mode", ["usp", "legacy", "compat", "yunchang"])
@@ -82,3 +82,9 @@ def test_attention_from_projections_two_ranks(U, R):
     """The processor slice (norm, rotary embedding, head split, USP, head merge) against the oracle:
     Ulysses 2 takes the fused send-buffer path, ring 2 the [B,H,s,D] hand-over to USP."""
     run_prologue(2, U, R, 29745 + R)
+
+
+def test_flux_joint_fp32_case_at_full_size_two_ranks():
+    """Ulysses 2, 24 heads x 128, 4096 image + 512 joint text tokens (rear), fp32, seed 0: the host logic at
+    the full shape (the stand-in attention is torch's fp32 CPU kernel here; the float64 oracle checks it)."""
+    run_flux_joint(2, 29761, tol=2e-5)

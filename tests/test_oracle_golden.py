@@ -258,3 +258,17 @@ def test_round_to_storage_matches_torch():
     np.testing.assert_array_equal(O.round_to_storage(x, "f16"), t.to(torch.float16).double().numpy())
     assert O.storage_ulp(1.0, "bf16") == 2.0 ** -7 and O.storage_ulp(5.0, "bf16") == 2.0 ** -5
     assert O.storage_ulp(1.0, "f16") == 2.0 ** -10
+
+
+def test_model_boundary_shard_and_gather_match_reference(golden_dir):
+    """`boundary_w4.npz`: the reference's `_chunk_and_pad_sequence` and `_gather_and_unpad` (on its real
+    `GroupCoordinator.all_gather`) under 4 gloo ranks, sequence lengths 10, 13, 9 and 8."""
+    z = np.load(os.path.join(golden_dir, "boundary_w4.npz"))
+    W = int(z["world"])
+    for name in z["names"]:
+        x, dim, pad = z[f"{name}_x"], int(z[f"{name}_dim"]), int(z[f"{name}_pad"])
+        chunks, got_pad = O.pad_and_shard_sequence(x, W, dim=dim)
+        assert got_pad == pad
+        np.testing.assert_array_equal(np.stack(chunks), z[f"{name}_chunks"])
+        np.testing.assert_array_equal(O.gather_and_unpad(chunks, pad, dim=dim), z[f"{name}_gathered"])
+        np.testing.assert_array_equal(z[f"{name}_gathered"], x)  # the round trip is the identity

@@ -158,6 +158,88 @@ def _yunchang_shaped_forward(xdit_b200, ql, kl, vl, kw, strat, rank, U, R, dev):
     return out
 
 
+def flux_joint_worker(rank, world, port, errq, backend="gloo", dtype_name="float32", tol=5e-5):
+    """USP at the Flux-shaped joint case at full size: Ulysses 2, B=1, 24 heads x 128, 4096 image tokens
+    sharded + 512 text tokens replicated (joint, rear), N(0,1) from seed 0, softmax scale 128^-1/2.  Every
+    rank's rows ``[image shard ; text]`` of two heads of each peer's head block are compared with the
+    oracle's dense attention (float64) over all 4608 keys."""
+    try:
+        sys.path.insert(0, ROOT)
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        gpu = backend == "nccl"
+        if gpu:
+            torch.cuda.set_device(rank)
+            dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        else:
+            dist.init_process_group("gloo", rank=rank, world_size=world)
+            torch.set_num_threads(4)
+        import xdit_b200
+        from oracle import usp_oracle as O
+
+        if not gpu:
+            from tests import fake_ops
+
+            fake_ops.install()
+            fake_ops.FAST_FP32 = True
+        dtype = getattr(torch, dtype_name)
+        dev = torch.device("cuda", rank) if gpu else torch.device("cpu")
+        xdit_b200.init_sequence_parallel(world, 1, backend=backend)
+        B, H, D, S, Sj = 1, 24, 128, 4096, 512
+        g = torch.Generator().manual_seed(0)
+        q, k, v = (torch.randn(B, H, S, D, generator=g) for _ in range(3))
+        jq, jk, jv = (torch.randn(B, H, Sj, D, generator=g) for _ in range(3))
+        cast = lambda t: t.to(dtype)
+        put = lambda t: cast(t).to(dev)
+        sh = lambda t: put(t.chunk(world, dim=2)[rank])
+        out = xdit_b200.USP(sh(q), sh(k), sh(v), joint_query=put(jq), joint_key=put(jk), joint_value=put(jv),
+                            joint_strategy="rear")
+        if gpu:
+            torch.cuda.synchronize()
+            from xdit_b200 import ops
+
+            ops.check_status()
+        s = S // world
+        assert tuple(out.shape) == (B, H, s + Sj, D)
+        heads = [0, H // world - 1, H // world, H - 1]  # first and last head of each peer's block
+        n64 = lambda t: cast(t).double().numpy()
+        qrows = torch.cat([q.chunk(world, dim=2)[rank], jq], dim=2)
+        want, _ = O.attention_dense(n64(qrows[:, heads]), n64(torch.cat([k, jk], 2)[:, heads]),
+                                    n64(torch.cat([v, jv], 2)[:, heads]))
+        got = out[:, heads].double().cpu().numpy()
+        err = float(np.abs(got - want).max())
+        cos = float((got * want).sum() / (np.linalg.norm(got) * np.linalg.norm(want)))
+        assert err < tol and cos >= 0.9999, ("flux joint case", rank, err, cos)
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception as e:
+        import traceback
+
+        errq.put(f"rank {rank}: {e}\n{traceback.format_exc()}")
+        raise
+
+
+def run_flux_joint(world, port, **kw):
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    errq = ctx.SimpleQueue()
+    procs = [ctx.Process(target=flux_joint_worker, args=(r, world, port, errq), kwargs=kw) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(600)
+    errs = []
+    while not errq.empty():
+        errs.append(errq.get())
+    for p in procs:
+        if p.is_alive():
+            p.terminate()
+            errs.append("a rank did not finish")
+    assert not errs and all(p.exitcode == 0 for p in procs), "\n".join(errs)
+
+
 def prologue_worker(rank, world, port, U, R, errq, backend="gloo", dtype_name="float32", tol=5e-5):
     """attention_from_projections under U x R ranks against the oracle: prologue on the global
     projections, dense attention, rows of this rank."""

@@ -27,6 +27,8 @@ EXPORTS = [
     "xdit_ulysses_unpack_out",
     "xdit_ulysses_unpack_in",
     "xdit_kv_patch_update",
+    "xdit_seq_shard_pad",
+    "xdit_seq_gather_unpad",
     "xdit_merge_out_lse",
     "xdit_qk_norm_rope_pack",
 ]
@@ -133,6 +135,12 @@ def load() -> C.CDLL:
         fn.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                        C.c_int32, C.c_void_p]
         fn.restype = C.c_int
+    lib.xdit_seq_shard_pad.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int32, C.c_int32,
+                                       C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]
+    lib.xdit_seq_shard_pad.restype = C.c_int
+    lib.xdit_seq_gather_unpad.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                          C.c_int32, C.c_int32, C.c_void_p]
+    lib.xdit_seq_gather_unpad.restype = C.c_int
     lib.xdit_kv_patch_update.argtypes = [C.POINTER(KvPatchParams), C.c_void_p]
     lib.xdit_kv_patch_update.restype = C.c_int
     lib.xdit_qk_norm_rope_pack.argtypes = [C.POINTER(PrologueParams), C.c_void_p]

@@ -219,6 +219,76 @@ int xdit_ulysses_unpack_in(const void* recv, void* dst, int32_t dtype, int32_t B
   return launch_row_copy(&r, 1, (cudaStream_t)stream);
 }
 
+int xdit_seq_shard_pad(const void* src, int64_t stride_b, int64_t stride_row, void* dst, int32_t dtype,
+                       int32_t B, int32_t S, int32_t C, int32_t W, int32_t rank, void* stream) {
+  const int es = dtype_size(dtype);
+  if (!es) { set_error("xdit_seq_shard_pad: bad dtype %d", dtype); return XDIT_E_DTYPE; }
+  if (!src || !dst) { set_error("xdit_seq_shard_pad: NULL pointer"); return XDIT_E_NULL; }
+  if (B < 1 || S < 1 || C < 1 || W < 1 || rank < 0 || rank >= W) {
+    set_error("xdit_seq_shard_pad: B=%d S=%d C=%d W=%d rank=%d", B, S, C, W, rank);
+    return XDIT_E_SHAPE;
+  }
+  const int s = (S + W - 1) / W;            // rows per rank after padding S up to a multiple of W
+  const int first = rank * s;
+  const int valid = first >= S ? 0 : (S - first < s ? S - first : s);
+  const int64_t row = (int64_t)C * es;
+  RowCopyJob rc[2];
+  int n = 0;
+  if (valid > 0) {
+    RowCopyJob& r = rc[n++];
+    r.src = (const char*)src + (int64_t)first * stride_row * es;
+    r.dst = (char*)dst;
+    r.n[0] = 1; r.n[1] = 1; r.n[2] = B; r.n[3] = valid;
+    r.s_stride[0] = 0; r.s_stride[1] = 0; r.s_stride[2] = stride_b * es; r.s_stride[3] = stride_row * es;
+    r.d_stride[0] = 0; r.d_stride[1] = 0; r.d_stride[2] = (int64_t)s * row; r.d_stride[3] = row;
+    r.row_bytes = (int32_t)row;
+  }
+  if (valid < s) {  // zero rows past the end of the sequence
+    RowCopyJob& r = rc[n++];
+    r.src = nullptr;
+    r.dst = (char*)dst + (int64_t)valid * row;
+    r.n[0] = 1; r.n[1] = 1; r.n[2] = B; r.n[3] = s - valid;
+    r.s_stride[0] = r.s_stride[1] = r.s_stride[2] = r.s_stride[3] = 0;
+    r.d_stride[0] = 0; r.d_stride[1] = 0; r.d_stride[2] = (int64_t)s * row; r.d_stride[3] = row;
+    r.row_bytes = (int32_t)row;
+  }
+  return launch_row_copy(rc, n, (cudaStream_t)stream);
+}
+
+int xdit_seq_gather_unpad(const void* recv, void* dst, int32_t dtype, int32_t W, int32_t B, int32_t s,
+                          int32_t C, int32_t keep, void* stream) {
+  const int es = dtype_size(dtype);
+  if (!es) { set_error("xdit_seq_gather_unpad: bad dtype %d", dtype); return XDIT_E_DTYPE; }
+  if (!recv || !dst) { set_error("xdit_seq_gather_unpad: NULL pointer"); return XDIT_E_NULL; }
+  if (W < 1 || B < 1 || s < 1 || C < 1 || keep < 1 || keep > (int64_t)W * s) {
+    set_error("xdit_seq_gather_unpad: W=%d B=%d s=%d C=%d keep=%d", W, B, s, C, keep);
+    return XDIT_E_SHAPE;
+  }
+  // recv [W][B][s][C] -> dst [B][keep][C]; source rank w contributes rows [w*s, min((w+1)*s, keep))
+  const int64_t row = (int64_t)C * es;
+  const int full = keep / s;          // ranks whose rows are all kept
+  const int tail = keep - full * s;   // kept rows of the next rank
+  RowCopyJob rc[2];
+  int n = 0;
+  if (full > 0) {
+    RowCopyJob& r = rc[n++];
+    r.src = (const char*)recv; r.dst = (char*)dst;
+    r.n[0] = 1; r.n[1] = full; r.n[2] = B; r.n[3] = s;
+    r.s_stride[0] = 0; r.s_stride[1] = (int64_t)B * s * row; r.s_stride[2] = (int64_t)s * row; r.s_stride[3] = row;
+    r.d_stride[0] = 0; r.d_stride[1] = (int64_t)s * row; r.d_stride[2] = (int64_t)keep * row; r.d_stride[3] = row;
+    r.row_bytes = (int32_t)row;
+  }
+  if (tail > 0) {
+    RowCopyJob& r = rc[n++];
+    r.src = (const char*)recv + (int64_t)full * B * s * row; r.dst = (char*)dst + (int64_t)full * s * row;
+    r.n[0] = 1; r.n[1] = 1; r.n[2] = B; r.n[3] = tail;
+    r.s_stride[0] = 0; r.s_stride[1] = 0; r.s_stride[2] = (int64_t)s * row; r.s_stride[3] = row;
+    r.d_stride[0] = 0; r.d_stride[1] = 0; r.d_stride[2] = (int64_t)keep * row; r.d_stride[3] = row;
+    r.row_bytes = (int32_t)row;
+  }
+  return launch_row_copy(rc, n, (cudaStream_t)stream);
+}
+
 int xdit_kv_patch_update(const struct xdit_kv_patch_params* p, void* stream) {
   if (!p) { set_error("xdit_kv_patch_update: NULL params"); return XDIT_E_NULL; }
   const int es = dtype_size(p->dtype);

@@ -34,7 +34,7 @@ inline int cuda_fail(cudaError_t e, const char* what) {
 // dst[i0,i1,i2,i3,:] = src[i0,i1,i2,i3,:] with per-dimension byte strides on both sides and
 // rows of row_bytes contiguous bytes.
 struct RowCopyJob {
-  const char* src;
+  const char* src;  // NULL: the destination rows are filled with zeros
   char* dst;
   int64_t s_stride[4];  // bytes
   int64_t d_stride[4];  // bytes

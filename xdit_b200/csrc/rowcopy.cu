@@ -52,6 +52,7 @@ __global__ void __launch_bounds__(kThreads) row_copy_kernel(const __grid_constan
     const int r0 = c3 * kRowsPerUnit;
     const int nrows = min(kRowsPerUnit, jb.n[3] - r0);
     const uint32_t nhb = min(hb, jb.n[1] - i1);
+    const bool zero = jb.src == nullptr;  // fill job (padding rows): nothing is read
     const char* s = jb.src + i0 * jb.s_stride[0] + i1 * jb.s_stride[1] + i2 * jb.s_stride[2] +
                     (int64_t)r0 * jb.s_stride[3];
     char* d = jb.dst + i0 * jb.d_stride[0] + i1 * jb.d_stride[1] + i2 * jb.d_stride[2] +
@@ -74,7 +75,7 @@ __global__ void __launch_bounds__(kThreads) row_copy_kernel(const __grid_constan
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         locate(idx + k * kThreads, so[k], dof[k]);
-        val[k] = __ldg(reinterpret_cast<const V*>(s + so[k]));
+        val[k] = zero ? V{} : __ldg(reinterpret_cast<const V*>(s + so[k]));
       }
 #pragma unroll
       for (int k = 0; k < 4; ++k) *reinterpret_cast<V*>(d + dof[k]) = val[k];
@@ -82,7 +83,7 @@ __global__ void __launch_bounds__(kThreads) row_copy_kernel(const __grid_constan
     for (; idx < nvec; idx += kThreads) {
       int64_t so, dof;
       locate(idx, so, dof);
-      *reinterpret_cast<V*>(d + dof) = __ldg(reinterpret_cast<const V*>(s + so));
+      *reinterpret_cast<V*>(d + dof) = zero ? V{} : __ldg(reinterpret_cast<const V*>(s + so));
     }
   }
 }
@@ -121,7 +122,7 @@ int launch_row_copy(const RowCopyJob* jobs, int njobs, cudaStream_t stream) {
     int64_t units = (int64_t)jb.n[0] * ((jb.n[1] + hb - 1) / hb) * jb.n[2];
     units *= (jb.n[3] + kRowsPerUnit - 1) / kRowsPerUnit;
     if (units <= 0 || jb.row_bytes <= 0) continue;  // empty job: nothing to move
-    if (!jb.src || !jb.dst) {
+    if (!jb.dst) {
       set_error("row copy: NULL pointer in job %d", j);
       return XDIT_E_NULL;
     }

@@ -314,6 +314,36 @@ def kv_patch_update(k_cache: torch.Tensor, v_cache: torch.Tensor, k_new: torch.T
     launch_count += 1
 
 
+def seq_shard_pad(x: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    """Rows of ``x`` [B, S, C] owned by sequence-parallel rank ``rank`` of ``world`` after zero-padding S
+    to a multiple of ``world``: a new contiguous [B, ceil(S/world), C] tensor (``xdit_seq_shard_pad``)."""
+    global launch_count
+    _require_cuda(x)
+    if x.dim() != 3 or (x.stride(2) != 1 and x.shape[2] != 1):
+        raise ValueError("expected [B, S, C] with a contiguous last axis")
+    B, S, Cn = x.shape
+    s = (S + world - 1) // world
+    dst = torch.empty(B, s, Cn, dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        _capi.check(_capi.load().xdit_seq_shard_pad(x.data_ptr(), x.stride(0), x.stride(1), dst.data_ptr(), _dtype(x),
+                                                    B, S, Cn, world, rank, _stream(x)), "xdit_seq_shard_pad")
+    launch_count += 1
+    return dst
+
+
+def seq_gather_unpad(recv: torch.Tensor, B: int, s: int, Cn: int, world: int, keep: int) -> torch.Tensor:
+    """``recv`` [world][B][s][C] (an all-gather's output) -> [B, keep, C] contiguous, the gathered sequence
+    without its ``world*s - keep`` padding rows (``xdit_seq_gather_unpad``)."""
+    global launch_count
+    _require_cuda(recv)
+    dst = torch.empty(B, keep, Cn, dtype=recv.dtype, device=recv.device)
+    with torch.cuda.device(recv.device):
+        _capi.check(_capi.load().xdit_seq_gather_unpad(recv.data_ptr(), dst.data_ptr(), _dtype(recv), world, B, s, Cn,
+                                                       keep, _stream(recv)), "xdit_seq_gather_unpad")
+    launch_count += 1
+    return dst
+
+
 def merge_out_lse(o_acc: torch.Tensor, lse_acc: torch.Tensor, out_b: torch.Tensor, lse_b: torch.Tensor,
                   first: bool, out_final: Optional[torch.Tensor] = None) -> None:
     """In-place online-softmax merge of (out_b, lse_b) into fp32 (o_acc, lse_acc)."""

@@ -65,11 +65,27 @@ def attention_from_projections(query: torch.Tensor, key: torch.Tensor, value: to
                                norm_k_weight: Optional[torch.Tensor] = None, eps: float = 1e-6,
                                norm_per_head: bool = False,
                                rotary_emb: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
-                               softmax_scale: Optional[float] = None) -> torch.Tensor:
+                               softmax_scale: Optional[float] = None,
+                               out_proj_weight: Optional[torch.Tensor] = None,
+                               out_proj_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Self-attention of one DiT layer from its q/k/v projections ``[B, s_local, heads*D]`` to the
     tensor the output projection takes, ``[B, s_local, heads*D]``, under the current sequence-parallel
     degrees.  With a Ulysses degree ``U > 1`` and no ring the prologue kernel writes straight into the
-    all-to-all send buffer; otherwise it produces ``[B, heads, s, D]`` tensors for ``USP``'s data path."""
+    all-to-all send buffer; otherwise it produces ``[B, heads, s, D]`` tensors for ``USP``'s data path.
+
+    With ``out_proj_weight`` (``[hidden, heads*D]``, optional bias) the layer's output projection
+    (``attn.to_out[0]``, ``transformer_wan.py:152``, ``transformer_flux.py:210-219``) is applied as well and
+    ``[B, s_local, hidden]`` is returned: the attention kernel writes its rows head-merged, so the
+    projection reads them where they lie."""
+    out = _attention_from_projections(query, key, value, heads, norm_q_weight, norm_k_weight, eps, norm_per_head,
+                                      rotary_emb, softmax_scale)
+    if out_proj_weight is not None:
+        out = torch.nn.functional.linear(out, out_proj_weight, out_proj_bias)
+    return out
+
+
+def _attention_from_projections(query, key, value, heads, norm_q_weight, norm_k_weight, eps, norm_per_head,
+                                rotary_emb, softmax_scale):
     B, s, HD = query.shape
     if HD % heads:
         raise ValueError("hidden size must be divisible by the number of heads")
