@@ -170,6 +170,11 @@ struct xdit_pack_job {
   void* dst;
   int64_t dst_peer_stride; /* elements between consecutive peers' blocks */
   int32_t s, s_joint, joint_front;
+  /* Packing a group of heads only (the exchange of one head group can then run while another group is
+   * being attended to): `H` of the call counts the group's heads over all peers, src / joint point at
+   * the group's first head of peer 0, and these give the distance in elements between the first heads
+   * of consecutive peers' blocks in src / joint.  0 selects (H/U) * stride_h, i.e. all heads. */
+  int64_t src_stride_peer, joint_stride_peer;
 };
 XDIT_API int xdit_ulysses_pack(const struct xdit_pack_job* jobs, int32_t njobs, int32_t dtype, int32_t B,
                       int32_t H, int32_t D, int32_t U, void* stream);

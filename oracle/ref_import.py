@@ -32,6 +32,19 @@ def seed_namespaces(ref_root: str) -> None:
         stub.__version__ = "0.35.2"
         stub.DiffusionPipeline = object
         sys.modules["diffusers"] = stub
+    # With a GPU present the reference's usp.py takes PROCESS_GROUP from the (un-vendored, absent) yunchang
+    # package at import time (usp.py:10-13); configure_usp() replaces that attribute anyway, so a bare
+    # holder is enough for the import.  A yunchang that is already importable is left alone.
+    if "yunchang" not in sys.modules:
+        try:
+            importlib.import_module("yunchang.globals")
+        except ImportError:
+            pkg, glob = types.ModuleType("yunchang"), types.ModuleType("yunchang.globals")
+            pkg.__path__ = []
+            glob.PROCESS_GROUP = type("PROCESS_GROUP", (), {"ULYSSES_PG": None, "RING_PG": None})
+            pkg.globals = glob
+            pkg.__xdit_b200_shim__ = glob.__xdit_b200_shim__ = True  # may be replaced by the package's own shim
+            sys.modules["yunchang"], sys.modules["yunchang.globals"] = pkg, glob
     for name in _NAMESPACES:
         if name not in sys.modules:
             mod = types.ModuleType(name)

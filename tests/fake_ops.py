@@ -50,7 +50,8 @@ def attn_fwd(q, k, v, k2=None, v2=None, *, out=None, lse=None, o_acc=None, lse_a
     return out, lse
 
 
-def ulysses_pack(items, U):
+def ulysses_pack(items, U, head_group=None):
+    g, G = head_group if head_group is not None else (0, 1)
     for it in items:
         src, joint, dst, stride = it["src"], it.get("joint"), it["dst"], it["peer_stride"]
         x = src
@@ -58,9 +59,10 @@ def ulysses_pack(items, U):
             x = torch.cat([joint, src], 2) if it.get("front") else torch.cat([src, joint], 2)
         B, H, rows, D = x.shape
         Hl = H // U
-        blk = Hl * B * rows * D
+        Hg = Hl // G
+        blk = Hg * B * rows * D
         for p in range(U):
-            part = x[:, p * Hl:(p + 1) * Hl].permute(1, 0, 2, 3).reshape(-1)
+            part = x[:, p * Hl + g * Hg:p * Hl + (g + 1) * Hg].permute(1, 0, 2, 3).reshape(-1)
             dst[p * stride:p * stride + blk].copy_(part)
 
 

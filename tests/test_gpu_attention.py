@@ -335,7 +335,8 @@ def test_timed_out_wait_is_reported_by_the_next_call(ops):
     ops.attn_fwd(q, k, v, out=sentinel, _wait_limit_ns=2_000_000, _selftest_stall=True)
     torch.cuda.synchronize()  # the launch ended by itself: the context is alive
     st = ops._status(q.device)
-    assert int(st.dev.item()) != 0 and int(st.host.item()) == int(st.dev.item())
+    # both words carry a code (each CTA that gave up writes its own; the device word keeps the first)
+    assert int(st.dev.item()) != 0 and int(st.host.item()) != 0
     assert torch.equal(sentinel, torch.full_like(q, 7.0))  # nothing was written
     with pytest.raises(_capi.XditError) as ei:
         ops.attn_fwd(q, k, v)

@@ -1,0 +1,152 @@
+"""PipeFusion stage-to-stage hand-off (xdit_b200.pipefusion) under 4 gloo ranks: a pipeline of four stages
+with stale-KV attention must produce, bit for bit, what one process computes when it runs all the layers
+itself with the same patch schedule (each layer's stale-KV buffer is only ever touched in patch order,
+so where a layer runs does not matter).  Kernels are the oracle-backed stand-ins here; the GPU twin runs
+the real kernels over NCCL."""
+import os
+import sys
+
+import pytest
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+
+B, HID, HEADS, S, NP, LAYERS_PER_STAGE, STEPS = 1, 32, 2, 48, 4, 2, 3
+
+
+def _layer_weights(layer, dtype, device):
+    g = torch.Generator().manual_seed(1000 + layer)
+    return [(torch.randn(HID, HID, generator=g) * 0.2).to(dtype).to(device) for _ in range(4)]
+
+
+def _make_stage(xdit_b200, layers, prefix, dtype, device):
+    mgr = xdit_b200.get_cache_manager()
+    weights = {l: _layer_weights(l, dtype, device) for l in layers}
+    for l in layers:
+        mgr.register_cache_entry(f"{prefix}{l}", "attn", "naive_cache")
+
+    def forward(x, step, p):
+        for l in layers:
+            wq, wk, wv, wo = weights[l]
+            heads = lambda t: t.unflatten(2, (HEADS, -1)).transpose(1, 2)
+            q, k, v = heads(x @ wq.T), heads(x @ wk.T), heads(x @ wv.T)
+            a = xdit_b200.USP(q, k, v, attn_layer=f"{prefix}{l}")
+            x = x + a.transpose(1, 2).flatten(2, 3) @ wo.T
+        return x
+
+    return forward
+
+
+def pipe_worker(rank, world, port, errq, backend="gloo", dtype_name="float32", tol=0.0):
+    try:
+        sys.path.insert(0, ROOT)
+        import torch.distributed as dist
+
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        gpu = backend == "nccl"
+        if gpu:
+            torch.cuda.set_device(rank)
+            dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        else:
+            dist.init_process_group("gloo", rank=rank, world_size=world)
+            torch.set_num_threads(1)
+        import xdit_b200
+        from xdit_b200.pipefusion import PatchPipe, run_async_steps
+
+        if not gpu:
+            from tests import fake_ops
+
+            fake_ops.install()
+        dtype = getattr(torch, dtype_name)
+        dev = torch.device("cuda", rank) if gpu else torch.device("cpu")
+        xdit_b200.init_sequence_parallel(1, 1)
+        rs = xdit_b200.initialize_runtime_state()
+        n = S // NP
+        rs.set_patches([n] * NP)
+        g = torch.Generator().manual_seed(7)
+        x0 = torch.randn(B, S, HID, generator=g).to(dtype).to(dev)
+        my_layers = list(range(rank * LAYERS_PER_STAGE, (rank + 1) * LAYERS_PER_STAGE))
+        stage = _make_stage(xdit_b200, my_layers, "pp", dtype, dev)
+        pipe = PatchPipe(None, [n] * NP, B, HID, dtype, dev)
+        assert pipe.is_first_stage == (rank == 0) and pipe.is_last_stage == (rank == world - 1)
+
+        # warm-up step: the full sequence through every stage, K/V buffers filled (patch mode off)
+        rs.set_patched_mode(False)
+        if rank == 0:
+            y = stage(x0, -1, 0)
+        else:
+            y = torch.empty_like(x0)
+            dist.recv(y, src=rank - 1)
+            y = stage(y, -1, 0)
+        if rank < world - 1:
+            dist.send(y.contiguous(), dst=rank + 1)
+        else:
+            dist.send(y.contiguous(), dst=0)  # the last stage hands the warm-up result round to the first
+        first_input = None
+        if rank == 0:
+            warm = torch.empty_like(x0)
+            dist.recv(warm, src=world - 1)
+            first_input = list(warm.split(n, dim=1))
+        last = run_async_steps(pipe, stage, STEPS, rs, first_input=first_input)
+        if gpu:
+            torch.cuda.synchronize()
+
+        if rank == world - 1:
+            # the same schedule with every layer in this process
+            ref_stage = _make_stage(xdit_b200, list(range(world * LAYERS_PER_STAGE)), "ref", dtype, dev)
+            rs.set_patched_mode(False)
+            cur = list(ref_stage(x0, -1, 0).split(n, dim=1))
+            rs.set_patched_mode(True)
+            for i in range(STEPS):
+                for p in range(NP):
+                    rs.pipeline_patch_idx = p
+                    cur[p] = ref_stage(cur[p], i, p)
+            rs.set_patched_mode(False)
+            for p in range(NP):
+                err = (last[p].double() - cur[p].double()).abs().max().item()
+                assert err <= tol, ("patch", p, err)
+            # the stage's input patches sit in one persistent [B, S, C] buffer, no concatenation
+            full = pipe.full_sequence()
+            assert full.shape == (B, S, HID) and full.data_ptr() == pipe.buffer.data_ptr()
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception as e:
+        import traceback
+
+        errq.put(f"rank {rank}: {e}\n{traceback.format_exc()}")
+        raise
+
+
+def run_pipe(world, port, **kw):
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    errq = ctx.SimpleQueue()
+    procs = [ctx.Process(target=pipe_worker, args=(r, world, port, errq), kwargs=kw) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+    errs = []
+    while not errq.empty():
+        errs.append(errq.get())
+    for p in procs:
+        if p.is_alive():
+            p.terminate()
+            errs.append("a rank did not finish")
+    assert not errs and all(p.exitcode == 0 for p in procs), "\n".join(errs)
+
+
+def test_four_stage_pipeline_equals_one_stage_on_cpu():
+    run_pipe(4, 29670)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("world", [2, 4])
+def test_pipeline_on_gpus(world):
+    """Real kernels (stale-KV patch update + attention) and NCCL point-to-point hand-off."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    run_pipe(world, 29680 + world, backend="nccl", dtype_name="float32", tol=1e-4)

@@ -60,9 +60,12 @@ def test_static_accumulators_match_caller_accumulators_twice(ops):
         want, want_lse = _ring_with_caller_buffers(ops, q, ks, vs, jk, jv)
         out = torch.empty_like(q)
         lse = torch.empty(B, H, Sq, dtype=torch.float32, device="cuda")
-        before = torch.cuda.memory_allocated()
+        # number of allocations made so far (a byte count would also move when the garbage collector
+        # frees an unrelated tensor in between)
+        count = lambda: torch.cuda.memory_stats().get("allocation.all.allocated", 0)
+        before = count()
         _ring_without_allocation(ops, q, ks, vs, jk, jv, out, lse)
-        assert torch.cuda.memory_allocated() == before  # the wrapper itself allocated nothing
+        assert count() == before  # the wrapper itself allocated nothing
         torch.cuda.synchronize()
         ops.check_status()
         # same kernel, same arithmetic: the tolerance of the suite is far looser than what we see

@@ -48,7 +48,14 @@ def worker(rank, world, port, files, mode, errq, backend="gloo", dtype_name="flo
             if strat:
                 kw = dict(joint_query=put(z["jq"]), joint_key=put(z["jk"]), joint_value=put(z["jv"]),
                           joint_strategy=strat)
-            if mode == "usp":
+            if mode == "usp_pipelined":
+                # the same call with the head-group pipeline forced on (it is size-gated in production)
+                import xdit_b200.usp as _usp_mod
+
+                _usp_mod.PIPELINE_MIN_BYTES = 0
+                ql, kl, vl = (t.transpose(1, 2).contiguous().transpose(1, 2) for t in (ql, kl, vl))
+                out = xdit_b200.USP(ql, kl, vl, **kw)
+            elif mode == "usp":
                 # transposed views, as the DiT processors pass them (transformer_flux.py:170-172)
                 ql, kl, vl = (t.transpose(1, 2).contiguous().transpose(1, 2) for t in (ql, kl, vl))
                 out = xdit_b200.USP(ql, kl, vl, **kw)

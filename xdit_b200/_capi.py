@@ -10,7 +10,8 @@ import ctypes as C
 import os
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "libxdit_b200.so")
+# XDIT_B200_LIB selects another build of the same library (same ABI), e.g. one compiled with other options
+LIB_PATH = os.environ.get("XDIT_B200_LIB") or os.path.join(_PKG, "libxdit_b200.so")
 
 XDIT_BF16, XDIT_F16, XDIT_F32 = 0, 1, 2
 XDIT_MAX_PACK_JOBS = 4
@@ -72,6 +73,7 @@ class PackJob(C.Structure):
         ("joint_stride_b", C.c_int64), ("joint_stride_h", C.c_int64), ("joint_stride_row", C.c_int64),
         ("dst", C.c_void_p), ("dst_peer_stride", C.c_int64),
         ("s", C.c_int32), ("s_joint", C.c_int32), ("joint_front", C.c_int32),
+        ("src_stride_peer", C.c_int64), ("joint_stride_peer", C.c_int64),
     ]
 
 

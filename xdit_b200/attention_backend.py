@@ -13,6 +13,8 @@ from __future__ import annotations
 
 from enum import Enum
 
+import torch
+
 from . import ops
 
 ATTENTION_FUNCTION_REGISTRY = {}
@@ -76,6 +78,10 @@ def b200_attn_call(query, key, value, dropout_p=0.0, is_causal=False, attention_
     if dropout_p:
         raise NotImplementedError("dropout is not implemented (the DiT callers always pass 0.0)")
     reject_masked(attention_kwargs)
+    if torch.compiler.is_compiling():
+        from . import compile_ops
+
+        return compile_ops.attn(query, key, value, None, None, bool(is_causal), 0.0)
     return ops.attn_fwd(query, key, value, causal=is_causal, want_lse=True)
 
 

@@ -111,7 +111,8 @@ int xdit_ulysses_pack(const struct xdit_pack_job* jobs, int32_t njobs, int32_t d
       r.src = (const char*)pj.src;
       r.dst = (char*)pj.dst + main_off * d_row;
       r.n[0] = U; r.n[1] = Hl; r.n[2] = B; r.n[3] = pj.s;
-      r.s_stride[0] = (int64_t)Hl * pj.src_stride_h * es; r.s_stride[1] = pj.src_stride_h * es;
+      r.s_stride[0] = (pj.src_stride_peer ? pj.src_stride_peer : (int64_t)Hl * pj.src_stride_h) * es;
+      r.s_stride[1] = pj.src_stride_h * es;
       r.s_stride[2] = pj.src_stride_b * es; r.s_stride[3] = pj.src_stride_row * es;
       r.d_stride[0] = d_p; r.d_stride[1] = d_h; r.d_stride[2] = d_b; r.d_stride[3] = d_row;
       r.row_bytes = D * es;
@@ -121,7 +122,8 @@ int xdit_ulysses_pack(const struct xdit_pack_job* jobs, int32_t njobs, int32_t d
       r.src = (const char*)pj.joint;
       r.dst = (char*)pj.dst + joint_off * d_row;
       r.n[0] = U; r.n[1] = Hl; r.n[2] = B; r.n[3] = pj.s_joint;
-      r.s_stride[0] = (int64_t)Hl * pj.joint_stride_h * es; r.s_stride[1] = pj.joint_stride_h * es;
+      r.s_stride[0] = (pj.joint_stride_peer ? pj.joint_stride_peer : (int64_t)Hl * pj.joint_stride_h) * es;
+      r.s_stride[1] = pj.joint_stride_h * es;
       r.s_stride[2] = pj.joint_stride_b * es; r.s_stride[3] = pj.joint_stride_row * es;
       r.d_stride[0] = d_p; r.d_stride[1] = d_h; r.d_stride[2] = d_b; r.d_stride[3] = d_row;
       r.row_bytes = D * es;

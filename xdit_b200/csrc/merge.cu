@@ -21,9 +21,38 @@ __device__ inline float logsigmoidf_(float x) {
   return fminf(x, 0.f) - log1pf(__expf(-fabsf(x)));
 }
 
+// Vector access helpers: VEC elements of the block's dtype / of fp32 in one load or store.
+template <typename T, int VEC> struct alignas(sizeof(T) * VEC) Pack { T v[VEC]; };
+template <typename T, int VEC>
+__device__ __forceinline__ void load_vec(const T* p, float (&out)[VEC]) {
+  if constexpr (VEC == 1) {
+    out[0] = to_f<T>(p[0]);
+  } else {
+    using P = Pack<T, VEC>;
+    const P x = *reinterpret_cast<const P*>(p);  // 8 bytes (16-bit types) or 16 bytes (fp32), aligned: D % 4 == 0
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) out[k] = to_f<T>(x.v[k]);
+  }
+}
+template <typename T, int VEC>
+__device__ __forceinline__ void store_vec(T* p, const float (&in)[VEC]) {
+  if constexpr (VEC == 1) {
+    p[0] = from_f<T>(in[0]);
+  } else {
+    Pack<T, VEC> x;
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) x.v[k] = from_f<T>(in[k]);
+    *reinterpret_cast<Pack<T, VEC>*>(p) = x;
+  }
+}
+
 // One group of LPR lanes (a power of two, at most a warp) owns a row: its lanes stride over the row's
 // vectors, and the row's lse is rewritten only after every lane of the warp has read it
-// (__syncwarp).  A row never spans warps, so no other thread reads lse_acc[r].
+// (__syncwarp).  A row never spans warps, so no other thread reads lse_acc[r].  A warp takes kRowsInFlight
+// row groups per iteration and issues all their loads before the arithmetic, which is what keeps enough
+// bytes in flight for an HBM-bound kernel.
+constexpr int kRowsInFlight = 4;
+
 template <typename T, int VEC>
 __global__ void __launch_bounds__(256) merge_kernel(float* __restrict__ o_acc, float* lse_acc,
                                                    const T* __restrict__ out_b,
@@ -37,51 +66,97 @@ __global__ void __launch_bounds__(256) merge_kernel(float* __restrict__ o_acc, f
   const int64_t warp_id = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
   const int64_t n_groups = (rows + rows_per_warp - 1) / rows_per_warp;
-  for (int64_t g = warp_id; g < n_groups; g += n_warps) {
-    const int64_t r = g * rows_per_warp + lane / lpr;
-    const bool live = r < rows;
-    float w = 0.f, lnew = 0.f;
-    if (live) {
-      const float lb = lse_b[r];
-      lnew = lb;
-      if (!first) {
-        const float la = lse_acc[r];
-        // both -inf (no keys seen on either side): keep the accumulator
-        if (la == -INFINITY && lb == -INFINITY) { w = 0.f; lnew = la; }
-        else { w = sigmoidf_(lb - la); lnew = la - logsigmoidf_(la - lb); }
+  const bool one_vec = vpr <= lpr;  // every lane has at most one vector of its row (D <= 128 with VEC 4)
+  for (int64_t g0 = warp_id * kRowsInFlight; g0 < n_groups; g0 += n_warps * kRowsInFlight) {
+    if (one_vec) {
+      int64_t r[kRowsInFlight];
+      bool live[kRowsInFlight];
+      float la[kRowsInFlight], lb[kRowsInFlight], ob[kRowsInFlight][VEC], oa[kRowsInFlight][VEC];
+#pragma unroll
+      for (int u = 0; u < kRowsInFlight; ++u) {
+        r[u] = (g0 + u) * rows_per_warp + lane / lpr;
+        live[u] = (g0 + u) < n_groups && r[u] < rows;
+        const bool mine = live[u] && sub < vpr;
+        la[u] = lb[u] = 0.f;
+        if (live[u]) {
+          lb[u] = lse_b[r[u]];
+          if (!first) la[u] = lse_acc[r[u]];
+        }
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) ob[u][k] = oa[u][k] = 0.f;
+        if (mine) {
+          const int64_t off = r[u] * D + (int64_t)sub * VEC;
+          load_vec<T, VEC>(out_b + off, ob[u]);
+          if (!first) load_vec<float, VEC>(o_acc + off, oa[u]);
+        }
       }
-      for (int v = sub; v < vpr; v += lpr) {
-        const int64_t off = r * D + (int64_t)v * VEC;
-        float res[VEC];
+      __syncwarp();  // every lane has read its rows' lse before any of them is rewritten
 #pragma unroll
-        for (int k = 0; k < VEC; ++k) {
-          const float ob = to_f<T>(out_b[off + k]);
-          if (first) res[k] = ob;
-          else { const float oa = o_acc[off + k]; res[k] = oa - w * (oa - ob); }
+      for (int u = 0; u < kRowsInFlight; ++u) {
+        if (!live[u]) continue;
+        float w = 0.f, lnew = lb[u];
+        if (!first) {
+          // both -inf (no keys seen on either side): keep the accumulator
+          if (la[u] == -INFINITY && lb[u] == -INFINITY) { w = 0.f; lnew = la[u]; }
+          else { w = sigmoidf_(lb[u] - la[u]); lnew = la[u] - logsigmoidf_(la[u] - lb[u]); }
         }
+        if (sub < vpr) {
+          const int64_t off = r[u] * D + (int64_t)sub * VEC;
+          float res[VEC];
 #pragma unroll
-        for (int k = 0; k < VEC; ++k) o_acc[off + k] = res[k];
-        if (out_final) {
-#pragma unroll
-          for (int k = 0; k < VEC; ++k) out_final[off + k] = from_f<T>(res[k]);
+          for (int k = 0; k < VEC; ++k) res[k] = first ? ob[u][k] : oa[u][k] - w * (oa[u][k] - ob[u][k]);
+          store_vec<float, VEC>(o_acc + off, res);
+          if (out_final) store_vec<T, VEC>(out_final + off, res);
         }
+        if (sub == 0) lse_acc[r[u]] = lnew;
+      }
+    } else {
+      // long rows (more vectors than lanes): one row group at a time, lanes stride over the row
+      for (int u = 0; u < kRowsInFlight; ++u) {
+        const int64_t g = g0 + u;
+        if (g >= n_groups) break;
+        const int64_t rr = g * rows_per_warp + lane / lpr;
+        const bool lv = rr < rows;
+        float w = 0.f, lnew = 0.f;
+        if (lv) {
+          const float lbv = lse_b[rr];
+          lnew = lbv;
+          if (!first) {
+            const float lav = lse_acc[rr];
+            if (lav == -INFINITY && lbv == -INFINITY) { w = 0.f; lnew = lav; }
+            else { w = sigmoidf_(lbv - lav); lnew = lav - logsigmoidf_(lav - lbv); }
+          }
+          for (int v = sub; v < vpr; v += lpr) {
+            const int64_t off = rr * D + (int64_t)v * VEC;
+            float obv[VEC], oav[VEC], res[VEC];
+            load_vec<T, VEC>(out_b + off, obv);
+            if (!first) load_vec<float, VEC>(o_acc + off, oav);
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) res[k] = first ? obv[k] : oav[k] - w * (oav[k] - obv[k]);
+            store_vec<float, VEC>(o_acc + off, res);
+            if (out_final) store_vec<T, VEC>(out_final + off, res);
+          }
+        }
+        __syncwarp();
+        if (lv && sub == 0) lse_acc[rr] = lnew;
       }
     }
-    __syncwarp();
-    if (live && sub == 0) lse_acc[r] = lnew;
   }
 }
 
 template <typename T>
 int launch(float* o_acc, float* lse_acc, const void* out_b, const float* lse_b, void* out_final,
            int64_t rows, int D, int first, cudaStream_t stream, int sms) {
-  const int vec = (D % 4 == 0) ? 4 : 1;
+  // vectors of 4 need 16-byte aligned fp32 rows and 8-byte (or 16-byte) aligned rows of the block
+  const bool aligned = D % 4 == 0 && (((uintptr_t)o_acc | (uintptr_t)out_b | (uintptr_t)out_final) & 15) == 0;
+  const int vec = aligned ? 4 : 1;
   const int vpr = D / vec;
   int lpr = 1;
   while (lpr < vpr && lpr < 32) lpr <<= 1;
-  const int64_t groups = (rows + (32 / lpr) - 1) / (32 / lpr);  // one warp each
-  int64_t blocks = (groups + 7) / 8;
-  if (blocks > (int64_t)sms * 16) blocks = (int64_t)sms * 16;
+  const int64_t groups = (rows + (32 / lpr) - 1) / (32 / lpr);
+  const int64_t warps = (groups + kRowsInFlight - 1) / kRowsInFlight;
+  int64_t blocks = (warps + 7) / 8;
+  if (blocks > (int64_t)sms * 32) blocks = (int64_t)sms * 32;
   if (blocks < 1) blocks = 1;
   if (vec == 4)
     merge_kernel<T, 4><<<(int)blocks, 256, 0, stream>>>(o_acc, lse_acc, (const T*)out_b, lse_b,

@@ -145,7 +145,6 @@ class xFuserLongContextAttention(torch.nn.Module):
         self.attn_processor = attn_processor
         self.ring_attn_fn = xdit_ring_flash_attn_func
 
-    @torch.compiler.disable
     def forward(self, attn, query: Tensor, key: Tensor, value: Tensor, *, joint_tensor_query=None,
                 joint_tensor_key=None, joint_tensor_value=None, dropout_p=0.0, softmax_scale=None, causal=False,
                 window_size=(-1, -1), alibi_slopes=None, deterministic=False, return_attn_probs=False,
@@ -168,9 +167,18 @@ class xFuserLongContextAttention(torch.nn.Module):
         elif any(given):
             raise ValueError(
                 "joint_tensor_query, joint_tensor_key, and joint_tensor_value should be None or not None simultaneously.")
+        t = lambda x: None if x is None else x.transpose(1, 2)
+        if (torch.compiler.is_compiling() and not self.use_kv_cache and self.ulysses_pg is PROCESS_GROUP.ULYSSES_PG
+                and self.ring_pg is PROCESS_GROUP.RING_PG):
+            # under torch.compile the call is one opaque operator (the reference disables compilation of
+            # this method altogether, hybrid/attn_layer.py:99)
+            from . import compile_ops
+
+            return compile_ops.usp(t(query), t(key), t(value), t(joint_tensor_query), t(joint_tensor_key),
+                                   t(joint_tensor_value), strategy or "", bool(causal),
+                                   float(softmax_scale) if softmax_scale else 0.0).transpose(1, 2)
         U, u_rank = _group_info(self.ulysses_pg)
         R, _ = _group_info(self.ring_pg)
-        t = lambda x: None if x is None else x.transpose(1, 2)
         out = _usp.usp_native(
             t(query), t(key), t(value), t(joint_tensor_query), t(joint_tensor_key), t(joint_tensor_value), strategy,
             attn if self.use_kv_cache else None, causal, softmax_scale, U, R, u_rank, self.ulysses_pg, self.ring_pg)

@@ -217,12 +217,15 @@ def attn_which(q, k, v, k2=None, v2=None, *, out=None, causal=False, acc=False) 
     return _capi.load().xdit_attn_which(C.byref(p))
 
 
-def ulysses_pack(items: Sequence[dict], U: int) -> None:
+def ulysses_pack(items: Sequence[dict], U: int, head_group=None) -> None:
     """Pack up to four tensors into all-to-all send buffers with one launch (``xdit_ulysses_pack``).
 
     Each item: ``src`` [B,H,s,D]; optional ``joint`` [B,H,sj,D] and ``front`` (bool); ``dst`` a
     1-D tensor positioned at this tensor's slot inside peer 0's block; ``peer_stride`` the
     distance in elements between two peers' blocks of that buffer.
+
+    ``head_group=(g, G)`` packs only group ``g`` of ``G`` equal groups of every peer's heads: peer p's
+    block then holds heads ``[p*H/U + g*H/(U*G), +H/(U*G))``.
     """
     global launch_count
     n = len(items)
@@ -231,6 +234,11 @@ def ulysses_pack(items: Sequence[dict], U: int) -> None:
     jobs = (_capi.PackJob * n)()
     ref = items[0]["src"]
     B, H, _, D = ref.shape
+    g, G = head_group if head_group is not None else (0, 1)
+    if H % (U * G):
+        raise ValueError("heads must divide into U peers x G groups")
+    Hl, Hg = H // U, H // (U * G)
+    es = ref.element_size()
     for j, it in zip(jobs, items):
         src, joint, dst = it["src"], it.get("joint"), it["dst"]
         _require_cuda(src, joint, dst)
@@ -238,20 +246,22 @@ def ulysses_pack(items: Sequence[dict], U: int) -> None:
             raise ValueError("tensors packed together must agree in dtype, B, H and D")
         if src.stride(3) != 1 and D != 1:
             raise ValueError("the head_dim axis must be contiguous")
-        j.src = src.data_ptr()
+        j.src = src.data_ptr() + g * Hg * src.stride(1) * es
         j.src_stride_b, j.src_stride_h, j.src_stride_row = src.stride(0), src.stride(1), src.stride(2)
+        j.src_stride_peer = Hl * src.stride(1) if G > 1 else 0
         j.s = src.shape[2]
         if joint is not None:
             if joint.stride(3) != 1 and D != 1:
                 raise ValueError("the head_dim axis must be contiguous")
-            j.joint = joint.data_ptr()
+            j.joint = joint.data_ptr() + g * Hg * joint.stride(1) * es
             j.joint_stride_b, j.joint_stride_h, j.joint_stride_row = joint.stride(0), joint.stride(1), joint.stride(2)
+            j.joint_stride_peer = Hl * joint.stride(1) if G > 1 else 0
             j.s_joint = joint.shape[2]
             j.joint_front = int(bool(it.get("front", False)))
         j.dst = dst.data_ptr()
         j.dst_peer_stride = int(it["peer_stride"])
     with torch.cuda.device(ref.device):
-        _capi.check(_capi.load().xdit_ulysses_pack(jobs, n, _dtype(ref), B, H, D, U, _stream(ref)),
+        _capi.check(_capi.load().xdit_ulysses_pack(jobs, n, _dtype(ref), B, U * Hg, D, U, _stream(ref)),
                     "xdit_ulysses_pack")
     launch_count += 1
 

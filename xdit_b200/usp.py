@@ -320,9 +320,125 @@ def USP(
     if dropout_p:
         raise NotImplementedError("dropout is not implemented (the DiT callers always pass 0.0)")
     reject_masked(attention_kwargs)
+    if torch.compiler.is_compiling() and not attn_layer:
+        # under torch.compile the whole call is one opaque operator (no graph break at the ctypes calls)
+        from . import compile_ops
+
+        return compile_ops.usp(query, key, value, joint_query, joint_key, joint_value, joint_strategy or "",
+                               bool(is_causal), 0.0)
     return usp_native(query, key, value, joint_query, joint_key, joint_value, joint_strategy, attn_layer,
                       is_causal, None, get_ulysses_parallel_world_size(), get_ring_parallel_world_size(),
                       get_ulysses_parallel_rank(), PROCESS_GROUP.ULYSSES_PG, PROCESS_GROUP.RING_PG)
+
+
+# Ulysses exchanges of at least this many bytes per rank are pipelined by head groups (see
+# _ulysses_pipelined); below it the extra collectives cost more than the overlap returns.
+PIPELINE_MIN_BYTES = 32 << 20
+_side_streams: dict = {}
+
+
+def _all_to_all_chunks(out_chunks, in_chunks, group) -> None:
+    """Equal-split all-to-all whose receive side is a list of separately placed chunks (the grouped
+    send/recv form of NCCL).  gloo has no such collective: there (host-logic tests on CPU) it is one flat
+    all-to-all and a copy."""
+    if in_chunks[0].is_cuda:
+        dist.all_to_all(out_chunks, in_chunks, group=group)
+        return
+    flat_in = torch.cat([c.reshape(-1) for c in in_chunks])
+    flat_out = torch.empty_like(flat_in)
+    dist.all_to_all_single(flat_out, flat_in, group=group)
+    for dst, src in zip(out_chunks, flat_out.chunk(len(out_chunks))):
+        dst.copy_(src.view_as(dst))
+
+
+class _TwoStreams:
+    """The current stream and one side stream of a CUDA device; on a CPU device (host-logic tests under
+    gloo) every operation is a no-op and the work simply runs in program order."""
+
+    def __init__(self, device):
+        self.cuda = device.type == "cuda"
+        if self.cuda:
+            key = device.index if device.index is not None else torch.cuda.current_device()
+            side = _side_streams.get(key)
+            if side is None:
+                side = _side_streams[key] = torch.cuda.Stream(device)
+            self.cur, self.side = torch.cuda.current_stream(device), side
+
+    def on(self, which):
+        import contextlib
+
+        if not self.cuda or which == 0:
+            return contextlib.nullcontext()
+        return torch.cuda.stream(self.side)
+
+    def side_waits_cur(self):
+        if self.cuda:
+            self.side.wait_stream(self.cur)
+
+    def cur_waits_side(self):
+        if self.cuda:
+            self.cur.wait_stream(self.side)
+
+    def keep_for_side(self, tensors):
+        if self.cuda:
+            for t in tensors:  # used on both streams: keep the allocator from recycling them early
+                t.record_stream(self.side)
+
+
+def _ulysses_pipelined(query, key, value, jq, jk, jv, front, scale, U, uly):
+    """Ulysses-only attention with the exchange hidden behind the arithmetic: every peer's heads are split
+    into two groups; group 1 is packed and exchanged on a side stream while group 0 is attended to, and
+    group 0's result travels back while group 1 is attended to (``usp.py:96-150`` does pack, collective,
+    attention, collective strictly one after the other).  The two return exchanges write interleaved
+    slices of one ``[H][B][rows][D]`` buffer, so the result is the same view as without pipelining."""
+    B, H, s, D = query.shape
+    sk = key.shape[2]
+    sj = jq.shape[2] if jq is not None else 0
+    sq = s + sj
+    Hl = H // U
+    Hg = Hl // 2
+    dev, dt = query.device, query.dtype
+    q_blk, kv_blk = Hg * B * sq * D, Hg * B * sk * D
+    stride = q_blk + 2 * kv_blk
+    ts = _TwoStreams(dev)
+    out_recv = torch.empty(H * B * sq * D, dtype=dt, device=dev)
+    out_chunks = out_recv.view(U, 2, q_blk)  # [peer][group][Hg*B*sq*D]
+    ts.side_waits_cur()  # the inputs are ready for the side stream too
+    recvs, sends, outs = [], [], []
+    for g in (0, 1):
+        with ts.on(g):
+            send = torch.empty(U * stride, dtype=dt, device=dev)
+            ops.ulysses_pack([
+                dict(src=query, joint=jq, front=front, dst=send, peer_stride=stride),
+                dict(src=key, dst=send[q_blk:], peer_stride=stride),
+                dict(src=value, dst=send[q_blk + kv_blk:], peer_stride=stride),
+            ], U, head_group=(g, 2))
+            sends.append(send)
+    for g in (0, 1):
+        with ts.on(g):
+            recv = torch.empty_like(sends[g])
+            dist.all_to_all_single(recv, sends[g], group=uly)
+            recvs.append(recv)
+    for g in (0, 1):
+        if g == 1:
+            ts.cur_waits_side()  # group 1 has arrived
+        recv = recvs[g]
+        q5 = recv.as_strided((B, Hg, U, sq, D), (sq * D, B * sq * D, stride, D, 1), 0)
+        shape, strides = (B, Hg, U, sk, D), (sk * D, B * sk * D, stride, D, 1)
+        k5, v5 = recv.as_strided(shape, strides, q_blk), recv.as_strided(shape, strides, q_blk + kv_blk)
+        out_send = torch.empty(U * q_blk, dtype=dt, device=dev)
+        out5 = out_send.as_strided((B, Hg, U, sq, D), (sq * D, B * sq * D, q_blk, D, 1), 0)
+        jkg = jk[:, g * Hg:(g + 1) * Hg] if jk is not None else None
+        jvg = jv[:, g * Hg:(g + 1) * Hg] if jv is not None else None
+        ops.attn_fwd(q5, k5, v5, jkg, jvg, out=out5, scale=scale)
+        outs.append(out_send)
+        if g == 0:
+            ts.side_waits_cur()  # group 0's result exists; it travels back under group 1's attention
+        with ts.on(1 - g):
+            _all_to_all_chunks(list(out_chunks[:, g].unbind(0)), list(out_send.view(U, q_blk).unbind(0)), uly)
+    ts.cur_waits_side()
+    ts.keep_for_side(sends + recvs + outs + [out_recv])
+    return out_recv.view(H, B, sq, D).permute(1, 0, 2, 3)
 
 
 def usp_native(query, key, value, joint_query, joint_key, joint_value, joint_strategy, attn_layer, is_causal,
@@ -357,6 +473,9 @@ def usp_native(query, key, value, joint_query, joint_key, joint_value, joint_str
         assert H % U == 0, "h must be divisible by world_size, got {} and {}".format(H, U)
         Hl = H // U
         q_blk, kv_blk = Hl * B * sq * D, Hl * B * sk * D
+        if (R == 1 and not attn_layer and not want_lse and not is_causal and Hl % 2 == 0
+                and U * (q_blk + 2 * kv_blk) * query.element_size() >= PIPELINE_MIN_BYTES):
+            return _ulysses_pipelined(query, key, value, jq, jk, jv, front, scale, U, uly)
         if R == 1:
             stride = q_blk + 2 * kv_blk
             send = torch.empty(U * stride, dtype=dt, device=dev)
