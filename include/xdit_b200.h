@@ -267,6 +267,13 @@ struct xdit_prologue_params {
   int64_t cos_sin_stride_row;
   void *dst_q, *dst_k, *dst_v;
   int64_t dst_q_peer_stride, dst_k_peer_stride, dst_v_peer_stride;
+  /* Placement inside a peer's block, per tensor (q, k, v): elements between consecutive heads and between
+   * consecutive batches of the destination; rows are always D elements apart.  0 selects the packed send
+   * layout [H/U][B][s][D] (head stride B*s*D, batch stride s*D).  Other values let a tensor land somewhere
+   * else in one pass, e.g. the fresh K and V rows of a PipeFusion patch straight in the layer's persistent
+   * [B,H,S,D] stale-KV buffers (dst = buffer + row_start*D, head stride S*D, batch stride H*S*D), which
+   * replaces the separate patch update of xdit_kv_patch_update for callers that own the projections. */
+  int64_t dst_stride_h[3], dst_stride_b[3];
 };
 XDIT_API int xdit_qk_norm_rope_pack(const struct xdit_prologue_params* p, void* stream);
 

@@ -99,11 +99,19 @@ def merge_out_lse(o_acc, lse_acc, out_b, lse_b, first, out_final=None):
 
 
 def qk_norm_rope_pack(q, k, v, heads, dst_q, dst_k, dst_v, peer_strides, U=1, *, norm_q_weight=None,
-                      norm_k_weight=None, eps=1e-6, norm_per_head=False, cos=None, sin=None):
+                      norm_k_weight=None, eps=1e-6, norm_per_head=False, cos=None, sin=None, dst_strides=None):
     n = lambda t: None if t is None else _np(t)
     outs = O.attention_prologue(_np(q), _np(k), _np(v), heads, n(norm_q_weight), n(norm_k_weight), eps,
                                 norm_per_head, n(cos), n(sin), U)
-    for o, dst, stride in zip(outs, (dst_q, dst_k, dst_v), peer_strides):
+    for i, (o, dst, stride) in enumerate(zip(outs, (dst_q, dst_k, dst_v), peer_strides)):
+        st = dst_strides[i] if dst_strides is not None else None
+        if st is not None and (st[0] or st[1]):
+            # o[p]: [Hl, B, s, D] -> rows at dst + hip*stride_h + b*stride_b + row*D
+            Hl, B, s, D = o[0].shape
+            for p in range(U):
+                view = dst[p * stride:].as_strided((Hl, B, s, D), (st[0], st[1], D, 1))
+                view.copy_(torch.from_numpy(o[p]).to(dst.dtype))
+            continue
         blk = o[0].size
         for p in range(U):
             dst[p * stride:p * stride + blk].copy_(torch.from_numpy(o[p].reshape(-1)).to(dst.dtype))

@@ -150,3 +150,72 @@ def test_pipeline_on_gpus(world):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     run_pipe(world, 29680 + world, backend="nccl", dtype_name="float32", tol=1e-4)
+
+
+def _stale_kv_case(device, dtype, heads, D, S, NP, seed=3):
+    """(projections per call, weights, tables) of a layer that sees a warm-up call on the full sequence and
+    then patch calls in the order 2, 0, 3."""
+    g = torch.Generator().manual_seed(seed)
+    n = S // NP
+    mk = lambda rows: tuple(torch.randn(1, rows, heads * D, generator=g).to(dtype).to(device) for _ in range(3))
+    w = (1 + 0.1 * torch.randn(heads * D, generator=g)).to(dtype).to(device)
+    ang = torch.rand(S, D // 2, generator=g) * 6.28
+    cos, sin = torch.cos(ang).repeat_interleave(2, 1).to(device), torch.sin(ang).repeat_interleave(2, 1).to(device)
+    return n, mk, w, cos, sin
+
+
+def _run_stale_kv_both_ways(device, dtype):
+    """attention_from_projections(..., attn_layer=...) -- the prologue kernel writes the patch's K/V rows
+    straight into the layer's stale-KV buffers -- against the two-step form: prologue to [B,H,n,D] tensors,
+    then USP(..., attn_layer=...) whose cache manager patches the buffers with a separate pass."""
+    import xdit_b200
+    from xdit_b200.prologue import attention_from_projections, qk_norm_rope_heads
+
+    heads, D, S, NP = 4, 32, 64, 4
+    n, mk, w, cos, sin = _stale_kv_case(device, dtype, heads, D, S, NP)
+    xdit_b200.init_sequence_parallel(1, 1)
+    rs = xdit_b200.initialize_runtime_state()
+    rs.set_patches([n] * NP)
+    mgr = xdit_b200.get_cache_manager()
+    mgr.register_cache_entry("fused", "attn", "naive_cache")
+    mgr.register_cache_entry("twostep", "attn", "naive_cache")
+    calls = [(None, mk(S))] + [(p, mk(n)) for p in (2, 0, 3)]
+    outs = []
+    for p, (q, k, v) in calls:
+        rs.set_patched_mode(p is not None)
+        if p is not None:
+            rs.pipeline_patch_idx = p
+        rows = slice(0, S) if p is None else slice(p * n, (p + 1) * n)
+        rot = (cos[rows][None, :, None, :], sin[rows][None, :, None, :])
+        a = attention_from_projections(q, k, v, heads, norm_q_weight=w, norm_k_weight=w, rotary_emb=rot,
+                                       attn_layer="fused")
+        qh, kh, vh = qk_norm_rope_heads(q, k, v, heads, norm_q_weight=w, norm_k_weight=w, rotary_emb=rot)
+        b = xdit_b200.USP(qh, kh, vh, attn_layer="twostep").transpose(1, 2).reshape(1, -1, heads * D)
+        outs.append((a, b))
+    rs.set_patched_mode(False)
+    kf, kt = mgr.cache["attn", "fused"], mgr.cache["attn", "twostep"]
+    return outs, (kf.k, kf.v), (kt.k, kt.v)
+
+
+def test_prologue_writes_patch_rows_into_stale_kv_buffers_on_cpu(monkeypatch):
+    from tests import fake_ops
+
+    fake_ops.install(monkeypatch)
+    outs, fused, twostep = _run_stale_kv_both_ways(torch.device("cpu"), torch.float32)
+    for a, b in outs:
+        assert torch.equal(a, b)
+    assert torch.equal(fused[0], twostep[0]) and torch.equal(fused[1], twostep[1])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_prologue_writes_patch_rows_into_stale_kv_buffers_on_gpu(dtype):
+    """Same kernels either way, so the two forms must agree bit for bit: outputs and buffer contents."""
+    from xdit_b200 import ops
+
+    outs, fused, twostep = _run_stale_kv_both_ways(torch.device("cuda"), dtype)
+    torch.cuda.synchronize()
+    ops.check_status()
+    for a, b in outs:
+        assert torch.equal(a, b)
+    assert torch.equal(fused[0], twostep[0]) and torch.equal(fused[1], twostep[1])

@@ -99,6 +99,7 @@ class PrologueParams(C.Structure):
         ("cos", C.c_void_p), ("sin", C.c_void_p), ("cos_sin_stride_row", C.c_int64),
         ("dst_q", C.c_void_p), ("dst_k", C.c_void_p), ("dst_v", C.c_void_p),
         ("dst_q_peer_stride", C.c_int64), ("dst_k_peer_stride", C.c_int64), ("dst_v_peer_stride", C.c_int64),
+        ("dst_stride_h", C.c_int64 * 3), ("dst_stride_b", C.c_int64 * 3),
     ]
 
 

@@ -105,6 +105,35 @@ class CacheManager:
         end = U * rs.pp_patches_token_start_idx_local[rs.pipeline_patch_idx + 1]
         return self._patch(entry, k, v, start, end, n_new)
 
+    def rows_for_producer(self, layer: Any, B: int, H: int, n_new: int, D: int, dtype, device,
+                          layer_type: str = "attn"):
+        """For a caller that produces the fresh K/V rows itself (the fused attention prologue): make sure
+        the layer's buffers exist and say where the ``n_new`` rows belong.  Returns ``(k_cache, v_cache,
+        row_start)``; the caller writes rows ``[row_start, row_start + n_new)`` of both and then attends to
+        the whole buffers.  Same bookkeeping as ``update_and_get_kv`` for a ``naive_cache`` entry
+        (``cache_manager.py:103-135``); Ulysses-sharded entries go through ``update_and_get_kv``."""
+        entry = self.cache[layer_type, layer]
+        if entry.cache_type != "naive_cache":
+            raise NotImplementedError("rows_for_producer serves naive_cache entries (no sequence parallelism)")
+        state_ready = runtime_state_is_initialized()
+        num_patch = get_runtime_state().num_pipeline_patch if state_ready else 1
+        patch_mode = get_runtime_state().patch_mode if state_ready else False
+        if num_patch == 1 or not patch_mode:
+            if entry.k is None or entry.k.shape != (B, H, n_new, D) or entry.k.dtype != dtype \
+                    or entry.k.device != device:
+                entry.k = torch.empty(B, H, n_new, D, dtype=dtype, device=device)
+                entry.v = torch.empty(B, H, n_new, D, dtype=dtype, device=device)
+            return entry.k, entry.v, 0
+        rs = get_runtime_state()
+        start = rs.pp_patches_token_start_idx_local[rs.pipeline_patch_idx]
+        end = rs.pp_patches_token_start_idx_local[rs.pipeline_patch_idx + 1]
+        if entry.k is None:
+            raise RuntimeError("KV cache updated in patch mode before a full-sequence (warm-up) step filled it")
+        if end - start != n_new:
+            raise RuntimeError(
+                f"The expanded size of the tensor ({end - start}) must match the existing size ({n_new})")
+        return entry.k, entry.v, start
+
     # ------------------------------------------------------------------ helpers
     @staticmethod
     def _as_4d(x: torch.Tensor) -> torch.Tensor:

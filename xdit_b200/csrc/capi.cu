@@ -156,8 +156,15 @@ int xdit_qk_norm_rope_pack(const struct xdit_prologue_params* p, void* stream) {
   const uintptr_t ptrs = (uintptr_t)p->q | (uintptr_t)p->k | (uintptr_t)p->v | (uintptr_t)p->dst_q |
                          (uintptr_t)p->dst_k | (uintptr_t)p->dst_v | (uintptr_t)p->norm_q_weight |
                          (uintptr_t)p->norm_k_weight | (uintptr_t)p->cos | (uintptr_t)p->sin;
-  const int64_t strides = p->q_stride_b | p->q_stride_row | p->k_stride_b | p->k_stride_row | p->v_stride_b |
-                          p->v_stride_row | p->dst_q_peer_stride | p->dst_k_peer_stride | p->dst_v_peer_stride;
+  int64_t strides = p->q_stride_b | p->q_stride_row | p->k_stride_b | p->k_stride_row | p->v_stride_b |
+                    p->v_stride_row | p->dst_q_peer_stride | p->dst_k_peer_stride | p->dst_v_peer_stride;
+  for (int i = 0; i < 3; ++i) {
+    if (p->dst_stride_h[i] < 0 || p->dst_stride_b[i] < 0) {
+      set_error("xdit_qk_norm_rope_pack: negative destination stride");
+      return XDIT_E_SHAPE;
+    }
+    strides |= p->dst_stride_h[i] | p->dst_stride_b[i];
+  }
   if ((ptrs & 15) || (strides & 7) || (p->cos && (p->cos_sin_stride_row & 3))) {
     set_error("xdit_qk_norm_rope_pack: pointers must be 16-byte aligned and strides multiples of 8 elements");
     return XDIT_E_ALIGN;

@@ -50,6 +50,8 @@ struct PrologueArgs {
   int64_t cs_stride_row;    // elements
   char* dst[3];
   int64_t dst_peer_stride[3];  // bytes
+  int64_t dst_stride_h[3];     // bytes between heads of a peer block
+  int64_t dst_stride_b[3];     // bytes between batches
   int32_t B, H, D, s, U;
   int32_t per_head;
   float eps;
@@ -67,15 +69,14 @@ __global__ void __launch_bounds__(kThreads, 3) qk_norm_rope_pack_kernel(const __
   const bool same_col = kThreads % vpd == 0;
   // Which head, column and destination slot a thread's k-th vector belongs to does not depend on the
   // token row: the integer divisions are done once here, not per vector and row.
-  int d0_k[kMaxVec], peer_k[kMaxVec];
-  int64_t slot_k[kMaxVec];  // byte offset of (head in peer, column) inside a peer block, row 0 of batch 0
+  int d0_k[kMaxVec], peer_k[kMaxVec], hip_k[kMaxVec];  // column, peer and head-in-peer of a thread's k-th vector
 #pragma unroll
   for (int k = 0; k < kMaxVec; ++k) {
     const int idx = threadIdx.x + k * kThreads;
     const int head = idx / vpd;
     d0_k[k] = (idx - head * vpd) * 8;
     peer_k[k] = head / Hl;
-    slot_k[k] = ((int64_t)(head - peer_k[k] * Hl) * a.B * a.s * a.D + d0_k[k]) * 2;
+    hip_k[k] = head - peer_k[k] * Hl;
   }
   // a CTA takes runs of kRowRun consecutive token rows: its 256-byte writes to one head then fall
   // next to each other and leave L2 as longer runs
@@ -83,7 +84,7 @@ __global__ void __launch_bounds__(kThreads, 3) qk_norm_rope_pack_kernel(const __
   for (int64_t run = blockIdx.x; run < nruns; run += gridDim.x)
   for (int64_t r = run * kRowRun; r < min(rows, (run + 1) * kRowRun); ++r) {
     const int b = (int)(r / a.s), row = (int)(r - (int64_t)b * a.s);
-    const int64_t row_off = ((int64_t)b * a.s + row) * a.D * 2;  // bytes from a head's first row to this one
+    const int64_t row_bytes = (int64_t)row * a.D * 2;  // bytes from a (batch, head)'s first row to this one
     // With D/8 dividing the block size every vector of a thread starts at the same column of its head,
     // so the thread needs one set of eight cos and sin values per token row for q and k alike.
     float cs_row[8], sn_row[8];
@@ -209,7 +210,8 @@ __global__ void __launch_bounds__(kThreads, 3) qk_norm_rope_pack_kernel(const __
           o.z = Cvt<T>::pack(x[4], x[5]);
           o.w = Cvt<T>::pack(x[6], x[7]);
         }
-        char* d = a.dst[tns] + peer_k[k] * a.dst_peer_stride[tns] + slot_k[k] + row_off;
+        char* d = a.dst[tns] + peer_k[k] * a.dst_peer_stride[tns] + hip_k[k] * a.dst_stride_h[tns] +
+                  b * a.dst_stride_b[tns] + row_bytes + d0_k[k] * 2;
         *reinterpret_cast<uint4*>(d) = o;
       }
     }
@@ -231,6 +233,8 @@ int launch_prologue(const xdit_prologue_params& p, cudaStream_t stream) {
     a.src_stride_row[i] = sr[i] * 2;
     a.dst[i] = (char*)dst[i];
     a.dst_peer_stride[i] = dp[i] * 2;
+    a.dst_stride_h[i] = (p.dst_stride_h[i] ? p.dst_stride_h[i] : (int64_t)p.B * p.s * p.D) * 2;
+    a.dst_stride_b[i] = (p.dst_stride_b[i] ? p.dst_stride_b[i] : (int64_t)p.s * p.D) * 2;
   }
   a.weight[0] = (const char*)p.norm_q_weight;
   a.weight[1] = (const char*)p.norm_k_weight;

@@ -375,13 +375,14 @@ def qk_norm_rope_pack(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, heads: 
                       dst_k: torch.Tensor, dst_v: torch.Tensor, peer_strides: Sequence[int], U: int = 1, *,
                       norm_q_weight: Optional[torch.Tensor] = None, norm_k_weight: Optional[torch.Tensor] = None,
                       eps: float = 1e-6, norm_per_head: bool = False, cos: Optional[torch.Tensor] = None,
-                      sin: Optional[torch.Tensor] = None) -> None:
+                      sin: Optional[torch.Tensor] = None, dst_strides: Optional[Sequence] = None) -> None:
     """RMSNorm(q, k) + rotary embedding + head split + Ulysses pack in one launch (``xdit_qk_norm_rope_pack``).
 
     ``q, k, v``: projections ``[B, s, heads*D]`` (any batch/row strides, e.g. column slices of a fused
     qkv projection).  ``dst_*``: 1-D tensors positioned at the tensor's slot inside peer 0's block of
     the send buffer, ``peer_strides`` the distance in elements between two peers' blocks.  ``cos, sin``:
-    fp32 ``[s, D]``.
+    fp32 ``[s, D]``.  ``dst_strides``: optional ``[(head_stride, batch_stride)] * 3`` in elements (``None`` or
+    zeros: the packed ``[H/U][B][s][D]`` layout), e.g. to write k and v straight into ``[B,H,S,D]`` buffers.
     """
     global launch_count
     _require_cuda(q, k, v, dst_q, dst_k, dst_v, norm_q_weight, norm_k_weight, cos, sin)
@@ -413,6 +414,10 @@ def qk_norm_rope_pack(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, heads: 
         dst_q=dst_q.data_ptr(), dst_k=dst_k.data_ptr(), dst_v=dst_v.data_ptr(),
         dst_q_peer_stride=int(peer_strides[0]), dst_k_peer_stride=int(peer_strides[1]),
         dst_v_peer_stride=int(peer_strides[2]))
+    if dst_strides is not None:
+        for i, st in enumerate(dst_strides):
+            if st is not None:
+                p.dst_stride_h[i], p.dst_stride_b[i] = int(st[0]), int(st[1])
     with torch.cuda.device(q.device):
         _capi.check(_capi.load().xdit_qk_norm_rope_pack(C.byref(p), _stream(q)), "xdit_qk_norm_rope_pack")
     launch_count += 1

@@ -67,7 +67,7 @@ def attention_from_projections(query: torch.Tensor, key: torch.Tensor, value: to
                                rotary_emb: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
                                softmax_scale: Optional[float] = None,
                                out_proj_weight: Optional[torch.Tensor] = None,
-                               out_proj_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+                               out_proj_bias: Optional[torch.Tensor] = None, attn_layer=None) -> torch.Tensor:
     """Self-attention of one DiT layer from its q/k/v projections ``[B, s_local, heads*D]`` to the
     tensor the output projection takes, ``[B, s_local, heads*D]``, under the current sequence-parallel
     degrees.  With a Ulysses degree ``U > 1`` and no ring the prologue kernel writes straight into the
@@ -76,12 +76,47 @@ def attention_from_projections(query: torch.Tensor, key: torch.Tensor, value: to
     With ``out_proj_weight`` (``[hidden, heads*D]``, optional bias) the layer's output projection
     (``attn.to_out[0]``, ``transformer_wan.py:152``, ``transformer_flux.py:210-219``) is applied as well and
     ``[B, s_local, hidden]`` is returned: the attention kernel writes its rows head-merged, so the
-    projection reads them where they lie."""
+    projection reads them where they lie.
+
+    ``attn_layer`` (PipeFusion, no sequence parallelism): the layer's stale-KV buffers are the attention's
+    keys and values, and the prologue kernel writes the fresh K and V rows of the current patch straight
+    into them -- no separate patch-update pass (``attention_processor.py:286-292`` ->
+    ``cache_manager.py:103-135``)."""
+    if attn_layer is not None:
+        out = _attention_with_stale_kv(query, key, value, heads, norm_q_weight, norm_k_weight, eps, norm_per_head,
+                                       rotary_emb, softmax_scale, attn_layer)
+        if out_proj_weight is not None:
+            out = torch.nn.functional.linear(out, out_proj_weight, out_proj_bias)
+        return out
     out = _attention_from_projections(query, key, value, heads, norm_q_weight, norm_k_weight, eps, norm_per_head,
                                       rotary_emb, softmax_scale)
     if out_proj_weight is not None:
         out = torch.nn.functional.linear(out, out_proj_weight, out_proj_bias)
     return out
+
+
+def _attention_with_stale_kv(query, key, value, heads, norm_q_weight, norm_k_weight, eps, norm_per_head, rotary_emb,
+                             softmax_scale, attn_layer):
+    from .cache_manager import get_cache_manager
+
+    if get_ulysses_parallel_world_size() * get_ring_parallel_world_size() != 1:
+        raise NotImplementedError("the fused stale-KV path serves PipeFusion without sequence parallelism; "
+                                  "use USP(..., attn_layer=...) otherwise")
+    B, n, HD = query.shape
+    D = HD // heads
+    kc, vc, start = get_cache_manager().rows_for_producer(attn_layer, B, heads, n, D, query.dtype, query.device)
+    S = kc.shape[2]
+    cos, sin = _cos_sin(rotary_emb, n, D)
+    q_buf = torch.empty(heads * B * n * D, dtype=query.dtype, device=query.device)
+    # q in the packed [H][B][n][D] layout; k and v rows at [start, start + n) of the [B,H,S,D] buffers
+    ops.qk_norm_rope_pack(query, key, value, heads, q_buf, kc.view(-1)[start * D:], vc.view(-1)[start * D:],
+                          (q_buf.numel(), 0, 0), 1, norm_q_weight=norm_q_weight, norm_k_weight=norm_k_weight, eps=eps,
+                          norm_per_head=norm_per_head, cos=cos, sin=sin,
+                          dst_strides=[None, (S * D, heads * S * D), (S * D, heads * S * D)])
+    q4 = q_buf.view(heads, B, n, D).permute(1, 0, 2, 3)
+    out = torch.empty(B, n, heads, D, dtype=query.dtype, device=query.device)
+    ops.attn_fwd(q4, kc, vc, out=out.permute(0, 2, 1, 3), scale=softmax_scale)
+    return out.view(B, n, HD)
 
 
 def _attention_from_projections(query, key, value, heads, norm_q_weight, norm_k_weight, eps, norm_per_head,
