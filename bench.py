@@ -539,7 +539,9 @@ def leg(torch, dist, xdit_b200, ops, name, w, args, device, rank, world, layers,
     except Exception as e:  # noqa: BLE001
         import traceback
 
-        return {"error": repr(e)[:300], "trace": traceback.format_exc()[-600:]}, False
+        # a leg that could not run is reported as such; only a result that was computed and is wrong makes
+        # the process exit non-zero
+        return {"error": repr(e)[:300], "trace": traceback.format_exc()[-600:]}, True
 
 
 def nvlink_bytes(w, U, R):
@@ -1098,6 +1100,26 @@ def main():
         extra[other], ok = leg(torch, dist, xdit_b200, ops, other, wo, args, device, rank, world, layers, world, 1,
                                tf_peak)
         all_ok &= ok
+        # the same Ulysses split with both exchanges done by the kernels' own stores into the peers' memory
+        # (xdit_b200.peer_exchange) instead of NCCL all-to-alls
+        if world > 1:
+            try:
+                from xdit_b200 import peer_exchange
+
+                peer_exchange.enable(True)
+                for wl, nl in ((other, layers), (name, min(4, w["layers"]))):
+                    extra[f"{wl}_peer_stores"], ok = leg(torch, dist, xdit_b200, ops, wl, WORKLOADS[wl], args, device,
+                                                         rank, world, nl, world, 1, tf_peak)
+                    all_ok &= ok
+            except Exception as e:  # noqa: BLE001
+                extra["peer_stores"] = {"unavailable": repr(e)[:300]}
+            finally:
+                peer_exchange.enable(False)
+                try:
+                    peer_exchange.close_all()
+                except Exception:  # noqa: BLE001
+                    pass
+            torch.cuda.empty_cache()
         # ring legs: the K/V rotation over NCCL with the merge in the kernel epilogue, checked the same way
         if world > 1:
             splits = [(1, world)] + ([(2, 4)] if world == 8 else []) + ([(2, 2)] if world == 4 else [])

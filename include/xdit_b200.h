@@ -119,7 +119,18 @@ struct xdit_attn_params {
    * stage un-armed, so that the consumer's bounded wait runs out after wait_limit_ns.  The launch
    * ends normally with the status words set and writes nothing to out. */
   int32_t selftest_stall;
+  /* Output of a Ulysses exchange written where it is needed: when not NULL, a host array of q.nseg
+   * device pointers; rows of query segment g go to out_segments[g] + b*out_stride_b + h*out_stride_h +
+   * row*out_stride_row (elements) and `out` / out_stride_seg are ignored.  A pointer may be a peer GPU's
+   * memory mapped into this process (xdit_peer_open): query segment g holds the rows of source rank g,
+   * so the kernel's epilogue can store every rank's result rows straight into that rank's [B, s, H, D]
+   * buffer with plain stores over NVLink -- the return all-to-all and the re-layout after it
+   * (xfuser/model_executor/layers/usp.py:138-150) disappear into the epilogue.  The caller orders the
+   * consumers on the other ranks after this launch (a collective or an event).  At most
+   * XDIT_MAX_OUT_SEGMENTS segments; served by the tcgen05 kernel only (XDIT_E_DTYPE otherwise). */
+  void* const* out_segments;
 };
+#define XDIT_MAX_OUT_SEGMENTS 16
 XDIT_API int xdit_attn_fwd(const struct xdit_attn_params* p, void* stream);
 /* Which kernel xdit_attn_fwd would run for these parameters: 1 = tcgen05/TMEM/TMA kernel,
  * 0 = CUDA-core kernel, negative = the error the call would return. */
@@ -178,6 +189,38 @@ struct xdit_pack_job {
 };
 XDIT_API int xdit_ulysses_pack(const struct xdit_pack_job* jobs, int32_t njobs, int32_t dtype, int32_t B,
                       int32_t H, int32_t D, int32_t U, void* stream);
+
+/* The same pack, but peer p's block is written at peer_base[p] + dst_offset[j] (elements) for job j
+ * instead of into one local send buffer: peer_base[p] is rank p's receive buffer mapped into this
+ * process (xdit_peer_open; the own rank's entry is a local pointer).  The send buffer, the NCCL
+ * all-to-all and its receive copy (usp.py:87-108) collapse into one pass of plain peer stores over NVLink.
+ * jobs[j].dst and dst_peer_stride are ignored.  The caller orders the readers on the other ranks after
+ * this launch. */
+XDIT_API int xdit_ulysses_pack_peers(const struct xdit_pack_job* jobs, int32_t njobs, int32_t dtype, int32_t B,
+                                     int32_t H, int32_t D, int32_t U, void* const* peer_base,
+                                     const int64_t* dst_offset, void* stream);
+
+/* Buffers that peer GPUs of the same node can store into (set-up, not hot path: these are the only entry
+ * points that allocate).  xdit_peer_alloc: a device buffer from cudaMalloc on the current device plus a
+ * 64-byte handle for other processes; xdit_peer_open: map a peer's buffer from its handle (enables peer
+ * access); xdit_peer_close / xdit_peer_free release them.  No counterpart in the reference, which moves
+ * everything through NCCL collectives. */
+#define XDIT_PEER_HANDLE_BYTES 64
+XDIT_API int xdit_peer_alloc(int64_t bytes, void** ptr, unsigned char* handle /*[XDIT_PEER_HANDLE_BYTES]*/);
+XDIT_API int xdit_peer_open(const unsigned char* handle, void** ptr);
+XDIT_API int xdit_peer_close(void* ptr);
+XDIT_API int xdit_peer_free(void* ptr);
+
+/* Barrier between the U ranks whose buffers are mapped into each other: rank `rank` stores its barrier
+ * count into word `rank` of every rank's flag array (peer_flags[r]: rank r's array of U uint32 words,
+ * mapped into this process; the own entry is local_flags) and waits until every word of local_flags has
+ * reached the same count.  `epoch` is a uint32 in this rank's device memory, zero at set-up, advanced by
+ * the kernel (so a captured launch replays).  The wait is bounded by wait_limit_ns (0: 2 s); when it runs
+ * out, *status / *status_host are set like xdit_attn_params.status / status_host (code 400 + the rank that
+ * did not arrive) and the kernel returns; while *status is non-zero barriers do not wait.  Every rank must
+ * call it the same number of times.  No counterpart in the reference. */
+XDIT_API int xdit_peer_barrier(void* const* peer_flags, void* local_flags, void* epoch, int32_t U, int32_t rank,
+                               uint32_t wait_limit_ns, int32_t* status, int32_t* status_host, void* stream);
 
 /* Ulysses output pack in the reference's own wire layout: [B,Hl,S,D] (any strides) ->
  * send buffer [S][B][Hl][D] contiguous (peer p's block = rows [p*S/U,(p+1)*S/U)), and the

@@ -362,3 +362,27 @@ def test_launch_after_a_failure_is_a_no_op_until_cleared(ops):
         ops.check_status()
     out, _ = _run(ops, q, k, v)
     compare(out, oracle_attn(q, k, v)[0], "after clearing")
+
+
+@pytest.mark.parametrize("D", [128, 64])
+def test_segment_outputs_to_separate_bases(ops, D):
+    """out_segments: the rows of query segment g go to a base address of their own, laid out
+    [B, rows, H_total, D] with this call's heads at a column offset -- what the epilogue does when it stores
+    every source rank's rows into that rank's result buffer.  Must equal the ordinary output bit for bit."""
+    B, Hl, G, L, Sk, Htot, hoff = 1, 3, 4, 200, 500, 12, 6
+    q = rand((B, Hl, G, L, D), torch.bfloat16, 60)
+    k, v = rand((B, Hl, Sk, D), torch.bfloat16, 61), rand((B, Hl, Sk, D), torch.bfloat16, 62)
+    want, _ = _run(ops, q, k, v)  # [B, Hl, G, L, D]
+    bufs = [torch.zeros(B, L, Htot, D, dtype=torch.bfloat16, device="cuda") for _ in range(G)]
+    segs = [b.data_ptr() + hoff * D * 2 for b in bufs]
+    ops.attn_fwd(q, k, v, out_segments=segs, out_strides=(L * Htot * D, D, Htot * D))
+    torch.cuda.synchronize()
+    ops.check_status()
+    for g in range(G):
+        got = bufs[g][:, :, hoff:hoff + Hl].permute(0, 2, 1, 3)  # [B, Hl, L, D]
+        assert torch.equal(got, want[:, :, g]), g
+        assert float(bufs[g][:, :, :hoff].abs().sum()) == 0 and float(bufs[g][:, :, hoff + Hl:].abs().sum()) == 0
+    from xdit_b200 import _capi
+
+    with pytest.raises(_capi.XditError):  # the CUDA-core kernel does not serve it
+        ops.attn_fwd(q.float(), k.float(), v.float(), out_segments=segs, out_strides=(L * Htot * D, D, Htot * D))

@@ -192,3 +192,76 @@ def test_merge_many_rows_whose_vectors_span_warps(ops, dtype, D, rows):
                                      np64(ob[idx]).reshape(1, 1, -1, D), np64(lb[idx]).reshape(1, 1, -1))
     np.testing.assert_allclose(np64(oa[idx]), want_o.reshape(-1, D), atol=2e-6, rtol=1e-5)
     np.testing.assert_allclose(np64(la[idx]), want_l.reshape(-1), atol=2e-6, rtol=1e-5)
+
+
+@pytest.mark.parametrize("front", [False, True])
+def test_pack_to_peer_bases_equals_pack_into_one_buffer(ops, front):
+    """xdit_ulysses_pack_peers with every "peer" buffer on this GPU: peer p's blocks must hold what
+    xdit_ulysses_pack puts at p * peer_stride of one send buffer (q with joint rows, k, v in one launch)."""
+    B, H, s, sj, sk, D, U = 1, 8, 100, 20, 130, 64, 4
+    q = rand((B, s, H, D), torch.bfloat16, 1).transpose(1, 2)
+    jq = rand((B, H, sj, D), torch.bfloat16, 2)
+    k, v = rand((B, H, sk, D), torch.bfloat16, 3), rand((B, H, sk, D), torch.bfloat16, 4)
+    Hl = H // U
+    q_blk, kv_blk = Hl * B * (s + sj) * D, Hl * B * sk * D
+    stride = q_blk + 2 * kv_blk
+    send = torch.zeros(U * stride, dtype=torch.bfloat16, device="cuda")
+    ops.ulysses_pack([dict(src=q, joint=jq, front=front, dst=send, peer_stride=stride),
+                      dict(src=k, dst=send[q_blk:], peer_stride=stride),
+                      dict(src=v, dst=send[q_blk + kv_blk:], peer_stride=stride)], U)
+    me = 2  # this rank's slot inside every peer's receive buffer
+    bufs = [torch.zeros(U * stride, dtype=torch.bfloat16, device="cuda") for _ in range(U)]
+    base = me * stride
+    ops.ulysses_pack_peers([dict(src=q, joint=jq, front=front, dst_offset=base),
+                            dict(src=k, dst_offset=base + q_blk),
+                            dict(src=v, dst_offset=base + q_blk + kv_blk)], U, [b.data_ptr() for b in bufs])
+    torch.cuda.synchronize()
+    for p in range(U):
+        assert torch.equal(bufs[p][base:base + stride], send[p * stride:(p + 1) * stride]), p
+        assert float(bufs[p][:base].abs().sum()) == 0 and float(bufs[p][base + stride:].abs().sum()) == 0
+
+
+def test_peer_buffer_alloc_view_free(ops):
+    ptr, handle, view = ops.peer_alloc(1 << 20, "cuda")
+    assert len(handle) == 64 and view.numel() == 1 << 20 and view.data_ptr() == ptr
+    t = view[:4096].view(torch.bfloat16)
+    t.fill_(1.5)
+    torch.cuda.synchronize()
+    assert float(t.float().sum()) == 1.5 * 2048
+    del t, view
+    ops.peer_free(ptr)
+
+
+def test_peer_barrier_passes_when_all_flags_arrived_and_reports_a_missing_rank(ops):
+    """xdit_peer_barrier as rank 0 of 2 on one GPU.  The other rank's flag word is written by hand (no second
+    kernel is ever made to wait for this one).  With the flag in place the barrier passes and bumps the epoch;
+    with the flag missing -- a word that nothing sets -- the wait runs out after 1 ms, the status words carry
+    400 + the missing rank, the context stays usable, and later barriers do not wait while the failure is
+    pending."""
+    from xdit_b200 import _capi
+
+    mine = torch.zeros(64, dtype=torch.int32, device="cuda")    # this rank's flag array
+    theirs = torch.zeros(64, dtype=torch.int32, device="cuda")  # stands for rank 1's array
+    epoch = torch.zeros(1, dtype=torch.int32, device="cuda")
+    flags = [mine.data_ptr(), theirs.data_ptr()]
+    mine[1] = 1  # rank 1 has arrived at barrier 1
+    ops.peer_barrier(flags, mine.data_ptr(), epoch, 0, "cuda", wait_limit_ns=1_000_000)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert int(epoch.item()) == 1 and int(mine[0].item()) == 1 and int(theirs[0].item()) == 1
+    mine[1] = 5  # a peer that is ahead also satisfies the wait
+    ops.peer_barrier(flags, mine.data_ptr(), epoch, 0, "cuda", wait_limit_ns=1_000_000)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert int(epoch.item()) == 2 and int(theirs[0].item()) == 2
+    mine[1] = 0  # rank 1 never arrives at barrier 3
+    ops.peer_barrier(flags, mine.data_ptr(), epoch, 0, "cuda", wait_limit_ns=1_000_000)
+    torch.cuda.synchronize()
+    st = ops._status("cuda")
+    assert int(st.dev.item()) == 401 and int(st.host.item()) == 401
+    assert int(theirs[0].item()) == 3  # its own flag was still posted
+    ops.peer_barrier(flags, mine.data_ptr(), epoch, 0, "cuda", wait_limit_ns=2_000_000_000)  # returns at once
+    torch.cuda.synchronize()
+    with pytest.raises(_capi.XditError, match="code 401"):
+        ops.check_status()
+    assert int(st.dev.item()) == 0 and int(st.host.item()) == 0

@@ -48,7 +48,17 @@ def worker(rank, world, port, files, mode, errq, backend="gloo", dtype_name="flo
             if strat:
                 kw = dict(joint_query=put(z["jq"]), joint_key=put(z["jk"]), joint_value=put(z["jv"]),
                           joint_strategy=strat)
-            if mode == "usp_pipelined":
+            if mode == "usp_peer":
+                # both Ulysses exchanges by direct stores into the peers' buffers (CUDA IPC mappings)
+                from xdit_b200 import peer_exchange
+
+                peer_exchange.enable(True)
+                ql, kl, vl = (t.transpose(1, 2).contiguous().transpose(1, 2) for t in (ql, kl, vl))
+                out = xdit_b200.USP(ql, kl, vl, **kw)
+                out2 = xdit_b200.USP(ql, kl, vl, **kw)  # second call: other result slot, same receive buffer
+                assert torch.equal(out, out2)
+                peer_exchange.enable(False)
+            elif mode == "usp_pipelined":
                 # the same call with the head-group pipeline forced on (it is size-gated in production)
                 import xdit_b200.usp as _usp_mod
 

@@ -15,6 +15,8 @@ LIB_PATH = os.environ.get("XDIT_B200_LIB") or os.path.join(_PKG, "libxdit_b200.s
 
 XDIT_BF16, XDIT_F16, XDIT_F32 = 0, 1, 2
 XDIT_MAX_PACK_JOBS = 4
+XDIT_MAX_OUT_SEGMENTS = 16
+XDIT_PEER_HANDLE_BYTES = 64
 XDIT_STATIC_ACC_FLOATS = 8 * 1024 * 1024
 
 EXPORTS = [
@@ -24,6 +26,12 @@ EXPORTS = [
     "xdit_attn_which",
     "xdit_attn_fwd_static_acc",
     "xdit_ulysses_pack",
+    "xdit_ulysses_pack_peers",
+    "xdit_peer_alloc",
+    "xdit_peer_open",
+    "xdit_peer_close",
+    "xdit_peer_free",
+    "xdit_peer_barrier",
     "xdit_ulysses_pack_out",
     "xdit_ulysses_unpack_out",
     "xdit_ulysses_unpack_in",
@@ -62,6 +70,7 @@ class AttnParams(C.Structure):
         ("softmax_scale", C.c_float), ("force_generic", C.c_int32),
         ("status", C.c_void_p),
         ("status_host", C.c_void_p), ("wait_limit_ns", C.c_uint32), ("selftest_stall", C.c_int32),
+        ("out_segments", C.POINTER(C.c_void_p)),
     ]
 
 
@@ -130,6 +139,21 @@ def load() -> C.CDLL:
     lib.xdit_ulysses_pack.argtypes = [C.POINTER(PackJob), C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                       C.c_int32, C.c_int32, C.c_void_p]
     lib.xdit_ulysses_pack.restype = C.c_int
+    lib.xdit_ulysses_pack_peers.argtypes = [C.POINTER(PackJob), C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                            C.c_int32, C.c_int32, C.POINTER(C.c_void_p), C.POINTER(C.c_int64),
+                                            C.c_void_p]
+    lib.xdit_ulysses_pack_peers.restype = C.c_int
+    lib.xdit_peer_alloc.argtypes = [C.c_int64, C.POINTER(C.c_void_p), C.c_char_p]
+    lib.xdit_peer_alloc.restype = C.c_int
+    lib.xdit_peer_open.argtypes = [C.c_char_p, C.POINTER(C.c_void_p)]
+    lib.xdit_peer_open.restype = C.c_int
+    lib.xdit_peer_close.argtypes = [C.c_void_p]
+    lib.xdit_peer_close.restype = C.c_int
+    lib.xdit_peer_free.argtypes = [C.c_void_p]
+    lib.xdit_peer_free.restype = C.c_int
+    lib.xdit_peer_barrier.argtypes = [C.POINTER(C.c_void_p), C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_uint32,
+                                      C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.xdit_peer_barrier.restype = C.c_int
     lib.xdit_ulysses_pack_out.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p,
                                           C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]
     lib.xdit_ulysses_pack_out.restype = C.c_int

@@ -16,7 +16,7 @@ CSRC = os.path.join(PKG, "csrc")
 INCLUDE = os.path.join(os.path.dirname(PKG), "include")
 LIB = os.path.join(PKG, "libxdit_b200.so")
 OBJ = os.path.join(PKG, "csrc", "_obj")
-SOURCES = ["capi.cu", "rowcopy.cu", "merge.cu", "attn_generic.cu", "attn_sm100.cu", "attn_static_acc.cu", "prologue.cu"]
+SOURCES = ["capi.cu", "rowcopy.cu", "merge.cu", "attn_generic.cu", "attn_sm100.cu", "attn_static_acc.cu", "prologue.cu", "peer_barrier.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",

@@ -58,6 +58,7 @@ struct alignas(64) Sm100Args {
   float scale_log2;
   void* out;
   int64_t out_stride_b, out_stride_h, out_stride_seg, out_stride_row;
+  void* out_seg[XDIT_MAX_OUT_SEGMENTS];  // per-segment output bases (possibly peer GPUs' memory); out == nullptr then
   float* lse;
   float* o_acc;
   float* lse_acc;
@@ -713,9 +714,12 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_sm100_kernel(const __gri
           }
         }
         unsigned char* orow = nullptr;
-        if (!a.acc_out)
-          orow = reinterpret_cast<unsigned char*>(a.out) +
-                 2 * (b * a.out_stride_b + h * a.out_stride_h + seg * a.out_stride_seg + trow * a.out_stride_row);
+        if (!a.acc_out) {
+          // one base per query segment when the rows go to their source ranks' buffers, else one tensor
+          unsigned char* obase = a.out ? reinterpret_cast<unsigned char*>(a.out) + 2 * seg * a.out_stride_seg
+                                       : reinterpret_cast<unsigned char*>(a.out_seg[seg]);
+          orow = obase + 2 * (b * a.out_stride_b + h * a.out_stride_h + trow * a.out_stride_row);
+        }
         float* arow = a.o_acc ? a.o_acc + flat * a.D : nullptr;
         for (int c0 = 0; c0 < a.dv_n; c0 += 32) {
           uint32_t o[32];
@@ -755,6 +759,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_sm100_kernel(const __gri
           if (a.acc_out) a.lse_acc[flat] = lse;
           else if (a.lse) a.lse[flat] = lse;
         }
+        if (!a.out && !a.acc_out) __threadfence_system();  // rows stored into peer GPUs' memory
       }
     }
   }
@@ -919,8 +924,11 @@ int attn_sm100_applicable(const xdit_attn_params& p) {
   if (!seq_ok(p.q, p.B, p.H, p.D, "q") || !seq_ok(p.k, p.B, p.H, p.D, "k") || !seq_ok(p.v, p.B, p.H, p.D, "v")) return 0;
   if (p.k2.ptr && (!seq_ok(p.k2, p.B, p.H, p.D, "k2") || !seq_ok(p.v2, p.B, p.H, p.D, "v2"))) return 0;
   if (!p.acc_out) {
-    if (((uintptr_t)p.out) & 15) { set_error("tcgen05 path: out pointer alignment"); return 0; }
-    if (p.out_stride_row % 8 || (p.q.nseg > 1 && p.out_stride_seg % 8) || (p.H > 1 && p.out_stride_h % 8) ||
+    if (p.out_segments) {
+      for (int g = 0; g < p.q.nseg; ++g)
+        if (((uintptr_t)p.out_segments[g]) & 15) { set_error("tcgen05 path: out_segments pointer alignment"); return 0; }
+    } else if (((uintptr_t)p.out) & 15) { set_error("tcgen05 path: out pointer alignment"); return 0; }
+    if (p.out_stride_row % 8 || (p.q.nseg > 1 && !p.out_segments && p.out_stride_seg % 8) || (p.H > 1 && p.out_stride_h % 8) ||
         (p.B > 1 && p.out_stride_b % 8)) { set_error("tcgen05 path: out strides"); return 0; }
   }
   if ((p.acc_in || p.acc_out) && ((((uintptr_t)p.o_acc) & 15) || (p.D % 4))) { set_error("tcgen05 path: o_acc alignment"); return 0; }
@@ -959,7 +967,9 @@ int launch_attn_sm100(const xdit_attn_params& p, cudaStream_t stream) {
   a.sq_total = p.q.nseg * p.q.seg_len;
   const float scale = p.softmax_scale > 0.f ? p.softmax_scale : 1.0f / sqrtf((float)p.D);
   a.scale_log2 = scale * 1.4426950408889634f;
-  a.out = p.out;
+  a.out = p.out_segments ? nullptr : p.out;
+  if (p.out_segments)
+    for (int g = 0; g < p.q.nseg && g < XDIT_MAX_OUT_SEGMENTS; ++g) a.out_seg[g] = p.out_segments[g];
   a.out_stride_b = p.out_stride_b; a.out_stride_h = p.out_stride_h;
   a.out_stride_seg = p.out_stride_seg; a.out_stride_row = p.out_stride_row;
   a.lse = p.lse; a.o_acc = p.o_acc; a.lse_acc = p.lse_acc;

@@ -2,6 +2,7 @@
 // domain-level parameters (Ulysses peers, joint rows, KV patches) into kernel launches.
 #include <cstdarg>
 #include <cstdio>
+#include <cstring>
 #include <mutex>
 
 #include "common.cuh"
@@ -72,30 +73,41 @@ int xdit_query_caps(struct xdit_caps* out) {
   return XDIT_OK;
 }
 
-int xdit_ulysses_pack(const struct xdit_pack_job* jobs, int32_t njobs, int32_t dtype, int32_t B,
-                      int32_t H, int32_t D, int32_t U, void* stream) {
+}  // extern "C"
+
+namespace xdit {
+// Shared body of xdit_ulysses_pack (one local send buffer, peers a fixed stride apart) and
+// xdit_ulysses_pack_peers (one base pointer per peer).
+static int pack_impl(const char* who, const struct xdit_pack_job* jobs, int32_t njobs, int32_t dtype, int32_t B,
+                     int32_t H, int32_t D, int32_t U, void* const* peer_base, const int64_t* dst_offset,
+                     void* stream) {
   const int es = dtype_size(dtype);
-  if (!es) { set_error("xdit_ulysses_pack: bad dtype %d", dtype); return XDIT_E_DTYPE; }
-  if (!jobs) { set_error("xdit_ulysses_pack: NULL jobs"); return XDIT_E_NULL; }
+  if (!es) { set_error("%s: bad dtype %d", who, dtype); return XDIT_E_DTYPE; }
+  if (!jobs) { set_error("%s: NULL jobs", who); return XDIT_E_NULL; }
   if (njobs < 1 || njobs > XDIT_MAX_PACK_JOBS) {
-    set_error("xdit_ulysses_pack: njobs=%d (1..%d)", njobs, XDIT_MAX_PACK_JOBS);
+    set_error("%s: njobs=%d (1..%d)", who, njobs, XDIT_MAX_PACK_JOBS);
     return XDIT_E_SHAPE;
   }
   if (B < 1 || H < 1 || D < 1 || U < 1 || H % U != 0) {
-    set_error("xdit_ulysses_pack: B=%d H=%d D=%d U=%d (H must be divisible by U)", B, H, D, U);
+    set_error("%s: B=%d H=%d D=%d U=%d (H must be divisible by U)", who, B, H, D, U);
     return XDIT_E_SHAPE;
   }
   const int Hl = H / U;
+  const int npeer_jobs = peer_base ? U : 1;  // with per-peer bases every peer is a row-copy job of its own
+  if (peer_base && njobs * 2 * U > kMaxRowCopyJobs) {
+    set_error("%s: %d tensors x %d peers exceed the %d copy jobs of one launch", who, njobs, U, kMaxRowCopyJobs);
+    return XDIT_E_SHAPE;
+  }
   RowCopyJob rc[kMaxRowCopyJobs];
   int n = 0;
   for (int j = 0; j < njobs; ++j) {
     const xdit_pack_job& pj = jobs[j];
     if (pj.s < 0 || pj.s_joint < 0 || pj.s + pj.s_joint == 0) {
-      set_error("xdit_ulysses_pack: job %d has s=%d s_joint=%d", j, pj.s, pj.s_joint);
+      set_error("%s: job %d has s=%d s_joint=%d", who, j, pj.s, pj.s_joint);
       return XDIT_E_SHAPE;
     }
-    if (!pj.dst || (pj.s && !pj.src) || (pj.s_joint && !pj.joint)) {
-      set_error("xdit_ulysses_pack: NULL pointer in job %d", j);
+    if ((!peer_base && !pj.dst) || (pj.s && !pj.src) || (pj.s_joint && !pj.joint)) {
+      set_error("%s: NULL pointer in job %d", who, j);
       return XDIT_E_NULL;
     }
     const int64_t rows = (int64_t)pj.s + pj.s_joint;
@@ -106,30 +118,94 @@ int xdit_ulysses_pack(const struct xdit_pack_job* jobs, int32_t njobs, int32_t d
     const int64_t d_p = pj.dst_peer_stride * es;
     const int main_off = pj.joint_front ? pj.s_joint : 0;
     const int joint_off = pj.joint_front ? 0 : pj.s;
-    if (pj.s) {
-      RowCopyJob& r = rc[n++];
-      r.src = (const char*)pj.src;
-      r.dst = (char*)pj.dst + main_off * d_row;
-      r.n[0] = U; r.n[1] = Hl; r.n[2] = B; r.n[3] = pj.s;
-      r.s_stride[0] = (pj.src_stride_peer ? pj.src_stride_peer : (int64_t)Hl * pj.src_stride_h) * es;
-      r.s_stride[1] = pj.src_stride_h * es;
-      r.s_stride[2] = pj.src_stride_b * es; r.s_stride[3] = pj.src_stride_row * es;
-      r.d_stride[0] = d_p; r.d_stride[1] = d_h; r.d_stride[2] = d_b; r.d_stride[3] = d_row;
-      r.row_bytes = D * es;
-    }
-    if (pj.s_joint) {
-      RowCopyJob& r = rc[n++];
-      r.src = (const char*)pj.joint;
-      r.dst = (char*)pj.dst + joint_off * d_row;
-      r.n[0] = U; r.n[1] = Hl; r.n[2] = B; r.n[3] = pj.s_joint;
-      r.s_stride[0] = (pj.joint_stride_peer ? pj.joint_stride_peer : (int64_t)Hl * pj.joint_stride_h) * es;
-      r.s_stride[1] = pj.joint_stride_h * es;
-      r.s_stride[2] = pj.joint_stride_b * es; r.s_stride[3] = pj.joint_stride_row * es;
-      r.d_stride[0] = d_p; r.d_stride[1] = d_h; r.d_stride[2] = d_b; r.d_stride[3] = d_row;
-      r.row_bytes = D * es;
+    const int64_t sp_main = (pj.src_stride_peer ? pj.src_stride_peer : (int64_t)Hl * pj.src_stride_h) * es;
+    const int64_t sp_joint = (pj.joint_stride_peer ? pj.joint_stride_peer : (int64_t)Hl * pj.joint_stride_h) * es;
+    for (int pp = 0; pp < npeer_jobs; ++pp) {
+      char* dbase;
+      if (peer_base) {
+        if (!peer_base[pp]) { set_error("%s: NULL base pointer for peer %d", who, pp); return XDIT_E_NULL; }
+        dbase = (char*)peer_base[pp] + dst_offset[j] * es;
+      } else {
+        dbase = (char*)pj.dst;
+      }
+      if (pj.s) {
+        RowCopyJob& r = rc[n++];
+        r.src = (const char*)pj.src + (peer_base ? pp * sp_main : 0);
+        r.dst = dbase + main_off * d_row;
+        r.n[0] = peer_base ? 1 : U; r.n[1] = Hl; r.n[2] = B; r.n[3] = pj.s;
+        r.s_stride[0] = sp_main; r.s_stride[1] = pj.src_stride_h * es;
+        r.s_stride[2] = pj.src_stride_b * es; r.s_stride[3] = pj.src_stride_row * es;
+        r.d_stride[0] = d_p; r.d_stride[1] = d_h; r.d_stride[2] = d_b; r.d_stride[3] = d_row;
+        r.row_bytes = D * es;
+      }
+      if (pj.s_joint) {
+        RowCopyJob& r = rc[n++];
+        r.src = (const char*)pj.joint + (peer_base ? pp * sp_joint : 0);
+        r.dst = dbase + joint_off * d_row;
+        r.n[0] = peer_base ? 1 : U; r.n[1] = Hl; r.n[2] = B; r.n[3] = pj.s_joint;
+        r.s_stride[0] = sp_joint; r.s_stride[1] = pj.joint_stride_h * es;
+        r.s_stride[2] = pj.joint_stride_b * es; r.s_stride[3] = pj.joint_stride_row * es;
+        r.d_stride[0] = d_p; r.d_stride[1] = d_h; r.d_stride[2] = d_b; r.d_stride[3] = d_row;
+        r.row_bytes = D * es;
+      }
     }
   }
-  return launch_row_copy(rc, n, (cudaStream_t)stream);
+  return launch_row_copy(rc, n, (cudaStream_t)stream, peer_base != nullptr);
+}
+}  // namespace xdit
+
+extern "C" {
+
+int xdit_ulysses_pack(const struct xdit_pack_job* jobs, int32_t njobs, int32_t dtype, int32_t B,
+                      int32_t H, int32_t D, int32_t U, void* stream) {
+  return pack_impl("xdit_ulysses_pack", jobs, njobs, dtype, B, H, D, U, nullptr, nullptr, stream);
+}
+
+int xdit_ulysses_pack_peers(const struct xdit_pack_job* jobs, int32_t njobs, int32_t dtype, int32_t B, int32_t H,
+                            int32_t D, int32_t U, void* const* peer_base, const int64_t* dst_offset, void* stream) {
+  if (!peer_base || !dst_offset) { set_error("xdit_ulysses_pack_peers: NULL peer_base / dst_offset"); return XDIT_E_NULL; }
+  return pack_impl("xdit_ulysses_pack_peers", jobs, njobs, dtype, B, H, D, U, peer_base, dst_offset, stream);
+}
+
+// ---- buffers that peer GPUs can store into (set-up path) ----------------------------------------
+int xdit_peer_alloc(int64_t bytes, void** ptr, unsigned char* handle) {
+  if (!ptr || !handle) { set_error("xdit_peer_alloc: NULL argument"); return XDIT_E_NULL; }
+  if (bytes < 1) { set_error("xdit_peer_alloc: bytes=%lld", (long long)bytes); return XDIT_E_SHAPE; }
+  static_assert(sizeof(cudaIpcMemHandle_t) == XDIT_PEER_HANDLE_BYTES, "handle size");
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, (size_t)bytes);
+  if (e != cudaSuccess) return cuda_fail(e, "xdit_peer_alloc: cudaMalloc");
+  cudaIpcMemHandle_t h;
+  e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) { cudaFree(p); return cuda_fail(e, "xdit_peer_alloc: cudaIpcGetMemHandle"); }
+  memcpy(handle, &h, sizeof(h));
+  *ptr = p;
+  return XDIT_OK;
+}
+
+int xdit_peer_open(const unsigned char* handle, void** ptr) {
+  if (!ptr || !handle) { set_error("xdit_peer_open: NULL argument"); return XDIT_E_NULL; }
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  void* p = nullptr;
+  cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) return cuda_fail(e, "xdit_peer_open: cudaIpcOpenMemHandle");
+  *ptr = p;
+  return XDIT_OK;
+}
+
+int xdit_peer_close(void* ptr) {
+  if (!ptr) return XDIT_OK;
+  cudaError_t e = cudaIpcCloseMemHandle(ptr);
+  if (e != cudaSuccess) return cuda_fail(e, "xdit_peer_close: cudaIpcCloseMemHandle");
+  return XDIT_OK;
+}
+
+int xdit_peer_free(void* ptr) {
+  if (!ptr) return XDIT_OK;
+  cudaError_t e = cudaFree(ptr);
+  if (e != cudaSuccess) return cuda_fail(e, "xdit_peer_free: cudaFree");
+  return XDIT_OK;
 }
 
 int xdit_qk_norm_rope_pack(const struct xdit_prologue_params* p, void* stream) {
@@ -365,7 +441,15 @@ int attn_check(const struct xdit_attn_params* p) {
     set_error("xdit_attn_fwd: acc_in/acc_out need o_acc and lse_acc");
     return XDIT_E_NULL;
   }
-  if (!p->acc_out && !p->out) { set_error("xdit_attn_fwd: NULL out"); return XDIT_E_NULL; }
+  if (!p->acc_out && !p->out && !p->out_segments) { set_error("xdit_attn_fwd: NULL out"); return XDIT_E_NULL; }
+  if (p->out_segments) {
+    if (p->q.nseg > XDIT_MAX_OUT_SEGMENTS) {
+      set_error("xdit_attn_fwd: out_segments with %d segments (at most %d)", p->q.nseg, XDIT_MAX_OUT_SEGMENTS);
+      return XDIT_E_SHAPE;
+    }
+    for (int g = 0; g < p->q.nseg; ++g)
+      if (!p->out_segments[g]) { set_error("xdit_attn_fwd: out_segments[%d] is NULL", g); return XDIT_E_NULL; }
+  }
   if (p->causal && (p->q.nseg != 1 || p->k.nseg != 1)) {
     set_error("xdit_attn_fwd: causal needs single-segment q and k");
     return XDIT_E_SHAPE;
@@ -401,6 +485,10 @@ int xdit_attn_fwd(const struct xdit_attn_params* p, void* stream) {
   if (rc) return rc;
   if (!p->force_generic && attn_sm100_applicable(*p) == 1)
     return launch_attn_sm100(*p, (cudaStream_t)stream);
+  if (p->out_segments) {
+    set_error("xdit_attn_fwd: out_segments is served by the tcgen05 kernel only (bf16/fp16, head_dim %% 8 == 0)");
+    return XDIT_E_DTYPE;
+  }
   return launch_attn_generic(*p, (cudaStream_t)stream);
 }
 

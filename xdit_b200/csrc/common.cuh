@@ -41,8 +41,9 @@ struct RowCopyJob {
   int32_t n[4];
   int32_t row_bytes;
 };
-constexpr int kMaxRowCopyJobs = 8;
-int launch_row_copy(const RowCopyJob* jobs, int njobs, cudaStream_t stream);
+constexpr int kMaxRowCopyJobs = 36;  // 4 tensors (+ joint rows) x up to 8 peers
+// system_fence: the destinations may be peer GPUs' memory; every thread ends with a system-scope fence.
+int launch_row_copy(const RowCopyJob* jobs, int njobs, cudaStream_t stream, bool system_fence = false);
 
 // ---- attention kernels ------------------------------------------------------------------------
 // Argument check shared by the attention entry points (bounds B, H, D and the sequence lengths).

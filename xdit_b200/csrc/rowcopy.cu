@@ -24,6 +24,7 @@ struct RowCopyArgs {
   int64_t unit_end[kMaxRowCopyJobs];  // exclusive prefix end of each job's units
   int32_t blk1[kMaxRowCopyJobs];      // how many consecutive i1 a unit covers
   int32_t njobs;
+  int32_t system_fence;
 };
 
 template <int VEC>
@@ -86,6 +87,7 @@ __global__ void __launch_bounds__(kThreads) row_copy_kernel(const __grid_constan
       *reinterpret_cast<V*>(d + dof) = zero ? V{} : __ldg(reinterpret_cast<const V*>(s + so));
     }
   }
+  if (args.system_fence) __threadfence_system();  // destinations in peer GPUs' memory
 }
 
 int pick_vec(const RowCopyJob* jobs, int njobs) {
@@ -103,7 +105,7 @@ int pick_vec(const RowCopyJob* jobs, int njobs) {
 
 }  // namespace
 
-int launch_row_copy(const RowCopyJob* jobs, int njobs, cudaStream_t stream) {
+int launch_row_copy(const RowCopyJob* jobs, int njobs, cudaStream_t stream, bool system_fence) {
   if (njobs <= 0 || njobs > kMaxRowCopyJobs) {
     set_error("row copy: %d jobs (1..%d supported)", njobs, kMaxRowCopyJobs);
     return XDIT_E_SHAPE;
@@ -134,6 +136,7 @@ int launch_row_copy(const RowCopyJob* jobs, int njobs, cudaStream_t stream) {
   }
   if (live == 0) return XDIT_OK;
   args.njobs = live;
+  args.system_fence = system_fence ? 1 : 0;
   int sms = 0;
   int rc = check_device(&sms);
   if (rc) return rc;

@@ -162,12 +162,16 @@ def _launch_attn(fn, p, q, where):
 
 def attn_fwd(q, k, v, k2=None, v2=None, *, out=None, lse=None, o_acc=None, lse_acc=None,
              acc_in=False, acc_out=False, causal=False, scale=None, force_generic=False,
-             want_lse=False, _wait_limit_ns=0, _selftest_stall=False):
+             want_lse=False, out_segments=None, out_strides=None, _wait_limit_ns=0, _selftest_stall=False):
     """Dense softmax attention forward (C-ABI ``xdit_attn_fwd``).
 
     Returns ``(out, lse)``.  ``out`` is allocated like ``q`` (contiguous, same dims) unless given;
     ``lse`` ([B,H,Sq] fp32) is produced when ``want_lse`` or when a buffer is passed.  With
     ``acc_out`` the result goes to the fp32 accumulators instead and ``out`` may stay ``None``.
+
+    ``out_segments`` (a list of ``q``'s segment count device addresses, possibly in peer GPUs' memory) with
+    ``out_strides = (batch, head, row)`` in elements sends the rows of every query segment to a base of its
+    own instead of one ``out`` tensor; nothing is returned for ``out`` then.
 
     Raises ``XditError`` (code ``XDIT_E_KERNEL_TIMEOUT``) when an earlier launch on this device gave
     up one of its bounded waits: that launch's output is invalid, nothing new was launched, and the
@@ -179,13 +183,22 @@ def attn_fwd(q, k, v, k2=None, v2=None, *, out=None, lse=None, o_acc=None, lse_a
         if t is not None and t.dtype != q.dtype:
             raise TypeError("q, k, v (and joint k, v) must share one dtype")
     sq = q.shape[2] if q.dim() == 4 else q.shape[2] * q.shape[3]
-    if out is None and not acc_out:
+    if out is None and not acc_out and out_segments is None:
         out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
     if lse is None and want_lse and not acc_out:
         lse = torch.empty(q.shape[0], q.shape[1], sq, dtype=torch.float32, device=q.device)
     p = _attn_params(q, k, v, k2, v2, out, lse, o_acc, lse_acc, acc_in, acc_out, causal, scale, force_generic)
     p.wait_limit_ns = int(_wait_limit_ns)
     p.selftest_stall = int(bool(_selftest_stall))
+    if out_segments is not None:
+        nseg = q.shape[2] if q.dim() == 5 else 1
+        if len(out_segments) != nseg or out_strides is None:
+            raise ValueError("out_segments needs one address per query segment and out_strides=(batch, head, row)")
+        seg_arr = (C.c_void_p * nseg)(*[int(x) for x in out_segments])
+        p.out_segments = C.cast(seg_arr, C.POINTER(C.c_void_p))
+        p.out = None
+        p.out_stride_b, p.out_stride_h, p.out_stride_row = (int(x) for x in out_strides)
+        p.out_stride_seg = 0
     _launch_attn(_capi.load().xdit_attn_fwd, p, q, "xdit_attn_fwd")
     launch_count += 1
     return out, lse
@@ -263,6 +276,95 @@ def ulysses_pack(items: Sequence[dict], U: int, head_group=None) -> None:
     with torch.cuda.device(ref.device):
         _capi.check(_capi.load().xdit_ulysses_pack(jobs, n, _dtype(ref), B, U * Hg, D, U, _stream(ref)),
                     "xdit_ulysses_pack")
+    launch_count += 1
+
+
+def ulysses_pack_peers(items: Sequence[dict], U: int, peer_base: Sequence[int]) -> None:
+    """Like :func:`ulysses_pack`, but peer p's block of item j is stored at ``peer_base[p] + dst_offset_j``
+    (``dst_offset`` in elements, an item key): the peers' receive buffers are written directly, over NVLink
+    for the other ranks (``xdit_ulysses_pack_peers``).  ``peer_base``: ``U`` device addresses."""
+    global launch_count
+    n = len(items)
+    if not 1 <= n <= _capi.XDIT_MAX_PACK_JOBS:
+        raise ValueError(f"1..{_capi.XDIT_MAX_PACK_JOBS} tensors per pack call")
+    if len(peer_base) != U:
+        raise ValueError("one base address per peer")
+    jobs = (_capi.PackJob * n)()
+    offs = (C.c_int64 * n)()
+    ref = items[0]["src"]
+    B, H, _, D = ref.shape
+    for i, (j, it) in enumerate(zip(jobs, items)):
+        src, joint = it["src"], it.get("joint")
+        _require_cuda(src, joint)
+        if src.dtype != ref.dtype or src.shape[0] != B or src.shape[1] != H or src.shape[3] != D:
+            raise ValueError("tensors packed together must agree in dtype, B, H and D")
+        if src.stride(3) != 1 and D != 1:
+            raise ValueError("the head_dim axis must be contiguous")
+        j.src = src.data_ptr()
+        j.src_stride_b, j.src_stride_h, j.src_stride_row = src.stride(0), src.stride(1), src.stride(2)
+        j.s = src.shape[2]
+        if joint is not None:
+            j.joint = joint.data_ptr()
+            j.joint_stride_b, j.joint_stride_h, j.joint_stride_row = joint.stride(0), joint.stride(1), joint.stride(2)
+            j.s_joint = joint.shape[2]
+            j.joint_front = int(bool(it.get("front", False)))
+        offs[i] = int(it["dst_offset"])
+    bases = (C.c_void_p * U)(*[int(x) for x in peer_base])
+    with torch.cuda.device(ref.device):
+        _capi.check(_capi.load().xdit_ulysses_pack_peers(jobs, n, _dtype(ref), B, H, D, U,
+                                                         C.cast(bases, C.POINTER(C.c_void_p)), offs, _stream(ref)),
+                    "xdit_ulysses_pack_peers")
+    launch_count += 1
+
+
+class _DeviceMemory:
+    """A raw device allocation presented through the CUDA array interface, so that torch can view it."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+def peer_alloc(nbytes: int, device) -> tuple:
+    """``(address, handle, uint8 tensor over it)`` of a buffer other processes of this node can map
+    (``xdit_peer_alloc``: cudaMalloc + an IPC handle).  Set-up path; free with :func:`peer_free`."""
+    ptr = C.c_void_p()
+    handle = C.create_string_buffer(_capi.XDIT_PEER_HANDLE_BYTES)
+    with torch.cuda.device(device):
+        _capi.check(_capi.load().xdit_peer_alloc(int(nbytes), C.byref(ptr), handle), "xdit_peer_alloc")
+        view = torch.as_tensor(_DeviceMemory(ptr.value, int(nbytes)), device=torch.device(device))
+    return ptr.value, handle.raw, view
+
+
+def peer_open(handle: bytes, device) -> int:
+    """Map a peer's buffer from its handle; returns the local address (``xdit_peer_open``)."""
+    ptr = C.c_void_p()
+    with torch.cuda.device(device):
+        _capi.check(_capi.load().xdit_peer_open(handle, C.byref(ptr)), "xdit_peer_open")
+    return ptr.value
+
+
+def peer_close(ptr: int) -> None:
+    _capi.check(_capi.load().xdit_peer_close(C.c_void_p(ptr)), "xdit_peer_close")
+
+
+def peer_free(ptr: int) -> None:
+    _capi.check(_capi.load().xdit_peer_free(C.c_void_p(ptr)), "xdit_peer_free")
+
+
+def peer_barrier(peer_flags: Sequence[int], local_flags: int, epoch: torch.Tensor, rank: int, device,
+                 wait_limit_ns: int = 0) -> None:
+    """Flag barrier over peer-mapped memory on the current stream (``xdit_peer_barrier``).  A wait that runs
+    out is reported like an attention kernel's: through the device's status words."""
+    global launch_count
+    U = len(peer_flags)
+    arr = (C.c_void_p * U)(*[int(x) for x in peer_flags])
+    st = _status(device)
+    with torch.cuda.device(device):
+        _capi.check(_capi.load().xdit_peer_barrier(C.cast(arr, C.POINTER(C.c_void_p)), C.c_void_p(int(local_flags)),
+                                                   C.c_void_p(epoch.data_ptr()), U, int(rank), int(wait_limit_ns),
+                                                   C.c_void_p(st.dev.data_ptr()), C.c_void_p(st.host.data_ptr()),
+                                                   torch.cuda.current_stream(torch.device(device)).cuda_stream),
+                    "xdit_peer_barrier")
     launch_count += 1
 
 

@@ -379,6 +379,18 @@ class _TwoStreams:
         if self.cuda:
             self.cur.wait_stream(self.side)
 
+    def mark_side(self):
+        """An event at the current end of the side stream (None on CPU)."""
+        if not self.cuda:
+            return None
+        ev = torch.cuda.Event()
+        ev.record(self.side)
+        return ev
+
+    def cur_waits_mark(self, ev):
+        if ev is not None:
+            self.cur.wait_event(ev)
+
     def keep_for_side(self, tensors):
         if self.cuda:
             for t in tensors:  # used on both streams: keep the allocator from recycling them early
@@ -419,9 +431,12 @@ def _ulysses_pipelined(query, key, value, jq, jk, jv, front, scale, U, uly):
             recv = torch.empty_like(sends[g])
             dist.all_to_all_single(recv, sends[g], group=uly)
             recvs.append(recv)
+    arrived1 = ts.mark_side()  # group 1 has arrived once the side stream gets here
     for g in (0, 1):
         if g == 1:
-            ts.cur_waits_side()  # group 1 has arrived
+            # only group 1's arrival is waited for: group 0's return exchange, queued on the side stream
+            # after it, keeps running under this group's attention
+            ts.cur_waits_mark(arrived1)
         recv = recvs[g]
         q5 = recv.as_strided((B, Hg, U, sq, D), (sq * D, B * sq * D, stride, D, 1), 0)
         shape, strides = (B, Hg, U, sk, D), (sk * D, B * sk * D, stride, D, 1)
@@ -439,6 +454,44 @@ def _ulysses_pipelined(query, key, value, jq, jk, jv, front, scale, U, uly):
     ts.cur_waits_side()
     ts.keep_for_side(sends + recvs + outs + [out_recv])
     return out_recv.view(H, B, sq, D).permute(1, 0, 2, 3)
+
+
+def _ulysses_peer_stores(query, key, value, jq, jk, jv, front, scale, U, u_rank, uly):
+    """Ulysses-only attention with both exchanges done by the kernels themselves (``xdit_b200.peer_exchange``):
+    the pack kernel stores every peer's block into that peer's receive buffer, the attention kernel's
+    epilogue stores every source rank's rows into that rank's ``[B, rows, H, D]`` result buffer.  Two
+    one-element all-reduces order the ranks.  Returns a ``[B, H, rows, D]`` view of the result buffer."""
+    from . import peer_exchange
+
+    B, H, s, D = query.shape
+    sk = key.shape[2]
+    sj = jq.shape[2] if jq is not None else 0
+    sq = s + sj
+    Hl = H // U
+    dt, es = query.dtype, query.element_size()
+    q_blk, kv_blk = Hl * B * sq * D, Hl * B * sk * D
+    stride = q_blk + 2 * kv_blk
+    ex = peer_exchange.get(uly, U * stride * es, B * sq * H * D * es, query.device)
+    # input side: my block for peer p lands at element offset u_rank*stride of p's receive buffer
+    base = u_rank * stride
+    ops.ulysses_pack_peers([
+        dict(src=query, joint=jq, front=front, dst_offset=base),
+        dict(src=key, dst_offset=base + q_blk),
+        dict(src=value, dst_offset=base + q_blk + kv_blk),
+    ], U, ex.in_peers())
+    ex.sync()
+    recv = ex.in_local(dt)
+    q5 = recv.as_strided((B, Hl, U, sq, D), (sq * D, B * sq * D, stride, D, 1), 0)
+    shape, strides = (B, Hl, U, sk, D), (sk * D, B * sk * D, stride, D, 1)
+    k5, v5 = recv.as_strided(shape, strides, q_blk), recv.as_strided(shape, strides, q_blk + kv_blk)
+    # output side: the rows of query segment g (source rank g) go to rank g's [B, sq, H, D] buffer, into
+    # the columns of this rank's heads
+    slot = ex.next_out_slot()
+    segs = [p + u_rank * Hl * D * es for p in ex.out_peers(slot)]
+    ops.attn_fwd(q5, k5, v5, jk, jv, out_segments=segs, out_strides=(sq * H * D, D, H * D), scale=scale)
+    ex.sync()
+    out = ex.out_local(slot, dt)[:B * sq * H * D].view(B, sq, H, D)
+    return out.permute(0, 2, 1, 3)
 
 
 def usp_native(query, key, value, joint_query, joint_key, joint_value, joint_strategy, attn_layer, is_causal,
@@ -473,6 +526,12 @@ def usp_native(query, key, value, joint_query, joint_key, joint_value, joint_str
         assert H % U == 0, "h must be divisible by world_size, got {} and {}".format(H, U)
         Hl = H // U
         q_blk, kv_blk = Hl * B * sq * D, Hl * B * sk * D
+        if (R == 1 and not attn_layer and not want_lse and not is_causal and query.is_cuda
+                and dt in (torch.bfloat16, torch.float16) and D % 8 == 0 and D <= 128 and U <= 16):
+            from . import peer_exchange
+
+            if peer_exchange.enabled_for(U * (q_blk + 2 * kv_blk) * query.element_size()):
+                return _ulysses_peer_stores(query, key, value, jq, jk, jv, front, scale, U, u_rank, uly)
         if (R == 1 and not attn_layer and not want_lse and not is_causal and Hl % 2 == 0
                 and U * (q_blk + 2 * kv_blk) * query.element_size() >= PIPELINE_MIN_BYTES):
             return _ulysses_pipelined(query, key, value, jq, jk, jv, front, scale, U, uly)
