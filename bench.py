@@ -411,7 +411,39 @@ def timed_region(torch, dist, fn, steps, warmup, device, multi):
     return ms
 
 
-def run_workload(torch, dist, xdit_b200, ops, name, w, args, device, rank, world, layers, with_e2e, U, R):
+def choose_exchange(torch, dist, xdit_b200, ops, inputs, device, want):
+    """Which form of the Ulysses exchange a leg uses.  ``want`` = "peer": direct stores into the peers'
+    buffers (xdit_b200.peer_exchange), kept only if one probing call succeeds on EVERY rank (the ranks agree
+    through an all-reduce, so they never take different paths); otherwise NCCL (pipelined by head groups for
+    large shards).  Returns (name, note)."""
+    from xdit_b200 import peer_exchange
+
+    if want != "peer":
+        peer_exchange.enable(False)
+        return "nccl", None
+    ok, note = 1.0, None
+    try:
+        peer_exchange.enable(True)
+        xdit_b200.USP(*inputs[0])
+        torch.cuda.synchronize(device)
+        ops.check_status()
+    except Exception as e:  # noqa: BLE001
+        ok, note = 0.0, repr(e)[:200]
+        try:
+            torch.cuda.synchronize(device)
+            ops.clear_status()
+        except Exception:  # noqa: BLE001
+            pass
+    t = torch.tensor([ok], dtype=torch.float32, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    if float(t.item()) < 1.0:
+        peer_exchange.enable(False)
+        return "nccl", note or "the probing call failed on another rank"
+    return "peer_stores", None
+
+
+def run_workload(torch, dist, xdit_b200, ops, name, w, args, device, rank, world, layers, with_e2e, U, R,
+                 exchange="nccl"):
     xdit_b200.init_sequence_parallel(U, R)
     P = U * R
     S = w["S"]
@@ -419,6 +451,11 @@ def run_workload(torch, dist, xdit_b200, ops, name, w, args, device, rank, world
     nsets = max(1, min(layers, w["sets"]))
     inputs = make_layer_inputs(torch, w, P, rank, nsets, device)
     multi = world > 1
+    exchange_note = None
+    if multi and U > 1 and R == 1:
+        exchange, exchange_note = choose_exchange(torch, dist, xdit_b200, ops, inputs, device, exchange)
+    else:
+        exchange = "none" if P == 1 else "nccl"
 
     # correctness first: one call, sampled rows against the oracle
     out = xdit_b200.USP(*inputs[0])
@@ -460,8 +497,10 @@ def run_workload(torch, dist, xdit_b200, ops, name, w, args, device, rank, world
         "launches": launches,
         "clocks": sampler.summary(),
         "U": U, "R": R, "layers": layers, "cuda_graph": graphed, "sets": nsets, "steps": args.steps,
-        "parity": parity,
+        "parity": parity, "exchange": exchange,
     }
+    if exchange_note:
+        res["exchange_note"] = exchange_note
     if with_e2e:
         host = make_layer_inputs(torch, w, P, rank, nsets, device, pinned=True)
         s = S // P
@@ -515,19 +554,27 @@ def run_workload(torch, dist, xdit_b200, ops, name, w, args, device, rank, world
                       "host_gbs_per_rank": (bytes_in + bytes_out) / (ms_e / e2e_steps * 1e-3) / 1e9}
         del host, host_out, slots
     del inputs
+    if exchange == "peer_stores":
+        from xdit_b200 import peer_exchange
+
+        peer_exchange.enable(False)
+        peer_exchange.close_all()  # every rank gets here: the groups of this leg are not used again
     torch.cuda.empty_cache()
     return res
 
 
-def leg(torch, dist, xdit_b200, ops, name, w, args, device, rank, world, layers, U, R, tf_peak, steps=3):
+def leg(torch, dist, xdit_b200, ops, name, w, args, device, rank, world, layers, U, R, tf_peak, steps=3,
+        exchange="nccl"):
     """A secondary measurement (another workload or another split): same timing rules, same parity
     check, a few layers or steps, no end-to-end part.  Never takes the main line down."""
     try:
         a2 = argparse.Namespace(steps=max(1, min(args.steps, steps)), warmup=3, graph=args.graph)
-        r = run_workload(torch, dist, xdit_b200, ops, name, w, a2, device, rank, world, layers, False, U, R)
+        r = run_workload(torch, dist, xdit_b200, ops, name, w, a2, device, rank, world, layers, False, U, R,
+                         exchange=exchange)
         P = U * R
         out = {
             "desc": w["desc"], "layers_timed": layers, "ulysses": U, "ring": R, "cuda_graph": r["cuda_graph"],
+            "exchange": r["exchange"],
             "tflops_all_gpus": r["tflops"], "tflops_per_gpu": r["tflops"] / world,
             "ms_per_layer_call": r["ms_per_step"] / layers,
             "frac_of_measured_bf16_burst_peak": r["tflops"] / world / tf_peak,
@@ -541,6 +588,13 @@ def leg(torch, dist, xdit_b200, ops, name, w, args, device, rank, world, layers,
 
         # a leg that could not run is reported as such; only a result that was computed and is wrong makes
         # the process exit non-zero
+        try:
+            from xdit_b200 import peer_exchange
+
+            peer_exchange.enable(False)
+            ops.clear_status()
+        except Exception:  # noqa: BLE001
+            pass
         return {"error": repr(e)[:300], "trace": traceback.format_exc()[-600:]}, True
 
 
@@ -1044,6 +1098,9 @@ def main():
                     help="also time one DiT forward of a random-init stand-in of this architecture (extra.dit_step)")
     ap.add_argument("--sp", default=None, help="override the sequence-parallel degrees of the main workload: ULYSSESxRING, e.g. 2x4")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end (host buffers) leg")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="Ulysses exchange at N > 1: stores into the peers' memory (kept only if a probing call "
+                         "succeeds on every rank) or NCCL all-to-alls")
     ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
                     help="replay the step as a CUDA graph (auto: only when N > 1, where the step is launch-bound)")
     args = ap.parse_args()
@@ -1090,7 +1147,7 @@ def main():
         U, R = (int(x) for x in args.sp.lower().split("x"))
         assert U * R == world, "--sp UxR must multiply to the number of GPUs"
     main_res = run_workload(torch, dist, xdit_b200, ops, name, w, args, device, rank, world, w["layers"],
-                            not args.no_e2e, U, R)
+                            not args.no_e2e, U, R, exchange=args.exchange)
     all_ok = main_res["parity"]["ok"]
     extra = {}
     if not args.no_extra:
@@ -1098,27 +1155,23 @@ def main():
         wo = WORKLOADS[other]
         layers = 4 if other == "wan" else wo["layers"]
         extra[other], ok = leg(torch, dist, xdit_b200, ops, other, wo, args, device, rank, world, layers, world, 1,
-                               tf_peak)
+                               tf_peak, exchange=args.exchange)
         all_ok &= ok
-        # the same Ulysses split with both exchanges done by the kernels' own stores into the peers' memory
-        # (xdit_b200.peer_exchange) instead of NCCL all-to-alls
+        # the same Ulysses split with the other form of the exchange (NCCL all-to-alls when the main legs
+        # use stores into the peers' memory, and the other way round), a few layers each
         if world > 1:
+            alt = "nccl" if main_res["exchange"] == "peer_stores" else "peer"
+            for wl, nl in ((other, min(layers, 19)), (name, min(4, w["layers"]))):
+                extra[f"{wl}_{'nccl' if alt == 'nccl' else 'peer_stores'}"], ok = leg(
+                    torch, dist, xdit_b200, ops, wl, WORKLOADS[wl], args, device, rank, world, nl, world, 1, tf_peak,
+                    exchange=alt)
+                all_ok &= ok
             try:
                 from xdit_b200 import peer_exchange
 
-                peer_exchange.enable(True)
-                for wl, nl in ((other, layers), (name, min(4, w["layers"]))):
-                    extra[f"{wl}_peer_stores"], ok = leg(torch, dist, xdit_b200, ops, wl, WORKLOADS[wl], args, device,
-                                                         rank, world, nl, world, 1, tf_peak)
-                    all_ok &= ok
-            except Exception as e:  # noqa: BLE001
-                extra["peer_stores"] = {"unavailable": repr(e)[:300]}
-            finally:
                 peer_exchange.enable(False)
-                try:
-                    peer_exchange.close_all()
-                except Exception:  # noqa: BLE001
-                    pass
+            except Exception:  # noqa: BLE001
+                pass
             torch.cuda.empty_cache()
         # ring legs: the K/V rotation over NCCL with the merge in the kernel epilogue, checked the same way
         if world > 1:
@@ -1188,6 +1241,7 @@ def main():
             "config": {
                 "workload": name, "desc": w["desc"], "step": f"{calls} USP attention calls (one per layer)",
                 "ulysses": main_res["U"], "ring": main_res["R"], "cuda_graph": main_res["cuda_graph"],
+                "exchange": main_res["exchange"], "exchange_note": main_res.get("exchange_note"),
                 "tokens": w["S"], "heads": w["H"],
                 "head_dim": w["D"], "global_batch": 1,
                 "l2": f"inputs larger than L2: {main_res['sets']} distinct q/k/v sets cycled layer by layer "
