@@ -1093,6 +1093,9 @@ def main():
     ap.add_argument("--workload", default="wan", choices=["flux", "wan"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary workloads, legs and the CPU baseline")
+    ap.add_argument("--extras", default="all",
+                    help="comma list of the legs to run under `extra`: other,alt_exchange,ring,hunyuan,pp,pixart,hbm,"
+                         "backends,dit,cpu (default: all)")
     ap.add_argument("--layers", type=int, default=0, help="time only this many layers per step (profiling aid)")
     ap.add_argument("--dit", default="both", choices=["none", "flux", "wan", "both"],
                     help="also time one DiT forward of a random-init stand-in of this architecture (extra.dit_step)")
@@ -1150,16 +1153,18 @@ def main():
                             not args.no_e2e, U, R, exchange=args.exchange)
     all_ok = main_res["parity"]["ok"]
     extra = {}
-    if not args.no_extra:
-        other = "wan" if name == "flux" else "flux"
+    want = (lambda k: True) if args.extras == "all" else (lambda k, sel=set(args.extras.split(",")): k in sel)
+    other = "wan" if name == "flux" else "flux"
+    layers = 4 if other == "wan" else WORKLOADS[other]["layers"]
+    if not args.no_extra and want("other"):
         wo = WORKLOADS[other]
-        layers = 4 if other == "wan" else wo["layers"]
         extra[other], ok = leg(torch, dist, xdit_b200, ops, other, wo, args, device, rank, world, layers, world, 1,
                                tf_peak, exchange=args.exchange)
         all_ok &= ok
+    if not args.no_extra:
         # the same Ulysses split with the other form of the exchange (NCCL all-to-alls when the main legs
         # use stores into the peers' memory, and the other way round), a few layers each
-        if world > 1:
+        if world > 1 and want("alt_exchange"):
             alt = "nccl" if main_res["exchange"] == "peer_stores" else "peer"
             for wl, nl in ((other, min(layers, 19)), (name, min(4, w["layers"]))):
                 extra[f"{wl}_{'nccl' if alt == 'nccl' else 'peer_stores'}"], ok = leg(
@@ -1174,7 +1179,7 @@ def main():
                 pass
             torch.cuda.empty_cache()
         # ring legs: the K/V rotation over NCCL with the merge in the kernel epilogue, checked the same way
-        if world > 1:
+        if world > 1 and want("ring"):
             splits = [(1, world)] + ([(2, 4)] if world == 8 else []) + ([(2, 2)] if world == 4 else [])
             for (u, r) in splits:
                 extra[f"wan_ring_u{u}r{r}"], ok = leg(torch, dist, xdit_b200, ops, "wan", WORKLOADS["wan"], args,
@@ -1182,11 +1187,11 @@ def main():
                 all_ok &= ok
         # the ring-dominant long-context case (119,056 tokens); ring degree = ranks, one GPU runs it dense
         wh = WORKLOADS["hunyuan"]
-        if wh["S"] % world == 0:
+        if wh["S"] % world == 0 and want("hunyuan"):
             extra["hunyuan_ring"], ok = leg(torch, dist, xdit_b200, ops, "hunyuan", wh, args, device, rank, world,
                                             2, 1, world, tf_peak, steps=2)
             all_ok &= ok
-        if world % 4 == 0:
+        if world % 4 == 0 and want("pp"):
             try:
                 extra["pixart_pipefusion_pp4"], ok = pixart_pipeline_leg(torch, dist, xdit_b200, ops, device, rank, world)
                 all_ok &= ok
@@ -1195,16 +1200,18 @@ def main():
 
                 extra["pixart_pipefusion_pp4"] = {"error": repr(e)[:300], "trace": traceback.format_exc()[-600:]}
             torch.cuda.empty_cache()
-        if world == 1:
+        if world == 1 and want("pixart"):
             try:
                 extra["pixart_pipefusion_steady"], ok = pixart_leg(torch, xdit_b200, ops, device, tf_peak)
                 all_ok &= ok
             except Exception as e:  # noqa: BLE001
                 extra["pixart_pipefusion_steady"] = {"error": repr(e)[:300]}
+        if world == 1 and want("hbm"):
             try:
                 extra["hbm_kernels"] = hbm_kernels(torch, ops, device, hbm_peak, peak_kind)
             except Exception as e:  # noqa: BLE001
                 extra["hbm_kernels"] = {"error": repr(e)[:200]}
+        if world == 1 and want("backends"):
             try:
                 ours_ms = {name: main_res["ms_per_step"] / w["layers"]}
                 if "ms_per_layer_call" in extra.get(other, {}):
@@ -1212,7 +1219,7 @@ def main():
                 extra["gpu_backends"] = gpu_backends(torch, device, ours_ms, tf_peak)
             except Exception as e:  # noqa: BLE001
                 extra["gpu_backends"] = {"error": repr(e)[:200]}
-        if args.dit != "none":
+        if args.dit != "none" and want("dit"):
             extra["dit_step"] = {}
             for kind in (("flux", "wan") if args.dit == "both" else (args.dit,)):
                 try:
@@ -1258,7 +1265,7 @@ def main():
         }
         if world > 1:
             line["nvlink"] = nvlink_bytes(w, main_res["U"], main_res["R"])
-        if world == 1 and not args.no_extra:
+        if world == 1 and not args.no_extra and want("cpu"):
             os.sched_setaffinity(0, cpus_before)  # the host baseline gets every core again
             line["cpu_baseline"] = cpu_baseline(w)
         print(json.dumps(line), flush=True)
