@@ -765,6 +765,55 @@ def pixart_leg(torch, xdit_b200, ops, device, tf_peak):
                        "against": "oracle dense attention over the patched K/V buffer"}}, ok
 
 
+def head_dim_legs(torch, ops, device, tf_peak):
+    """The tcgen05 kernel at the other head dims the reference's models use: 64 (SD3 / CogVideoX: 24 heads,
+    8192 tokens here) and 72 (PixArt: 16 heads over the full 16,384 tokens of a 2048 x 2048 image), dense,
+    one GPU, several input sets cycled so that K and V come from HBM; sampled rows against the oracle."""
+    import numpy as np
+
+    from oracle import usp_oracle as O
+
+    res, all_ok = {}, True
+    for label, H, S, D, sets in (("d64_h24_s8192", 24, 8192, 64, 8), ("d72_h16_s16384", 16, 16384, 72, 4)):
+        g = torch.Generator(device=device)
+        g.manual_seed(D)
+        ins = [tuple(torch.randn(1, H, S, D, generator=g, device=device).to(torch.bfloat16) for _ in range(3))
+               for _ in range(sets)]
+        out = torch.empty_like(ins[0][0])
+        for q, k, v in ins[:3]:
+            ops.attn_fwd(q, k, v, out=out)
+        q, k, v = ins[0]
+        ops.attn_fwd(q, k, v, out=out)
+        torch.cuda.synchronize(device)
+        f64 = lambda t: t.float().cpu().double().numpy()
+        rows = [0, S // 2, S - 64]
+        got = np.concatenate([f64(out[:, :2, r:r + 64]) for r in rows], axis=2)
+        want = np.concatenate([O.attention_dense(f64(q[:, :2, r:r + 64]), f64(k[:, :2]), f64(v[:, :2]))[0]
+                               for r in rows], axis=2)
+        max_abs = float(np.abs(got - want).max())
+        cos = float((got * want).sum() / (np.linalg.norm(got) * np.linalg.norm(want)))
+        ok = max_abs <= TOL_MAX_ABS and cos >= TOL_COS
+        all_ok &= ok
+        reps = 5
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            for q, k, v in ins:
+                ops.attn_fwd(q, k, v, out=out)
+        e1.record()
+        torch.cuda.synchronize(device)
+        ops.check_status()
+        ms = e0.elapsed_time(e1) / (reps * sets)
+        tf = 4.0 * S * S * H * D / (ms * 1e-3) / 1e12
+        res[label] = {"heads": H, "tokens": S, "head_dim": D, "ms_per_call": ms, "tflops_per_gpu": tf,
+                      "frac_of_measured_bf16_burst_peak": tf / tf_peak,
+                      "l2": f"{sets} input sets of {3 * H * S * D * 2 / 1e6:.0f} MB cycled",
+                      "parity": {"max_abs": max_abs, "cos": cos, "rows": 384, "ok": ok}}
+        del ins, out
+        torch.cuda.empty_cache()
+    return res, all_ok
+
+
 def pixart_pipeline_leg(torch, dist, xdit_b200, ops, device, rank, world, steps=3):
     """PixArt-Sigma 2048x2048 with PipeFusion across GPUs, as a random-init stand-in: 28 blocks (hidden 1152,
     16 heads x 72, text cross-attention to 300 tokens, MLP x4) cut into 4 pipeline stages of 7 blocks, 16,384
@@ -1094,7 +1143,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary workloads, legs and the CPU baseline")
     ap.add_argument("--extras", default="all",
-                    help="comma list of the legs to run under `extra`: other,alt_exchange,ring,hunyuan,pp,pixart,hbm,"
+                    help="comma list of the legs to run under `extra`: other,alt_exchange,ring,hunyuan,pp,pixart,head_dims,hbm,"
                          "backends,dit,cpu (default: all)")
     ap.add_argument("--layers", type=int, default=0, help="time only this many layers per step (profiling aid)")
     ap.add_argument("--dit", default="both", choices=["none", "flux", "wan", "both"],
@@ -1206,6 +1255,12 @@ def main():
                 all_ok &= ok
             except Exception as e:  # noqa: BLE001
                 extra["pixart_pipefusion_steady"] = {"error": repr(e)[:300]}
+        if world == 1 and want("head_dims"):
+            try:
+                extra["head_dims"], ok = head_dim_legs(torch, ops, device, tf_peak)
+                all_ok &= ok
+            except Exception as e:  # noqa: BLE001
+                extra["head_dims"] = {"error": repr(e)[:300]}
         if world == 1 and want("hbm"):
             try:
                 extra["hbm_kernels"] = hbm_kernels(torch, ops, device, hbm_peak, peak_kind)

@@ -194,11 +194,12 @@ def test_merge_many_rows_whose_vectors_span_warps(ops, dtype, D, rows):
     np.testing.assert_allclose(np64(la[idx]), want_l.reshape(-1), atol=2e-6, rtol=1e-5)
 
 
+@pytest.mark.parametrize("U", [4, 8, 16])
 @pytest.mark.parametrize("front", [False, True])
-def test_pack_to_peer_bases_equals_pack_into_one_buffer(ops, front):
+def test_pack_to_peer_bases_equals_pack_into_one_buffer(ops, front, U):
     """xdit_ulysses_pack_peers with every "peer" buffer on this GPU: peer p's blocks must hold what
     xdit_ulysses_pack puts at p * peer_stride of one send buffer (q with joint rows, k, v in one launch)."""
-    B, H, s, sj, sk, D, U = 1, 8, 100, 20, 130, 64, 4
+    B, H, s, sj, sk, D = 1, 16, 100, 20, 130, 64
     q = rand((B, s, H, D), torch.bfloat16, 1).transpose(1, 2)
     jq = rand((B, H, sj, D), torch.bfloat16, 2)
     k, v = rand((B, H, sk, D), torch.bfloat16, 3), rand((B, H, sk, D), torch.bfloat16, 4)

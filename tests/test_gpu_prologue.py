@@ -124,6 +124,23 @@ def test_model_shapes(ops, H, D, per_head, U):
     _check(ops, q, k, v, H, U, wq, wk, 1e-6, per_head, cos, sin, f"H{H} D{D} U{U}")
 
 
+@pytest.mark.parametrize("H,D,per_head,U,s", [
+    (1, 8, False, 1, 5), (4, 128, True, 2, 37), (12, 64, False, 3, 64), (12, 128, True, 1, 41), (16, 128, False, 4, 33),
+    (20, 128, False, 5, 29), (48, 64, True, 2, 23), (32, 128, False, 1, 19), (48, 128, False, 3, 17),
+    (64, 128, True, 8, 13), (2, 256, True, 1, 31), (9, 72, False, 3, 27), (32, 72, False, 2, 21), (64, 72, False, 1, 9),
+    (40, 128, False, 2, 3)])
+def test_every_row_width(ops, H, D, per_head, U, s):
+    """One case per compiled width of the kernel (vectors per lane 1..32), head dims whose vectors do not line
+    up with the lanes (72), and row counts that leave warps of the last CTA without a row."""
+    B = 2
+    q, k, v = (rand((B, s, H * D), torch.bfloat16, 30 + i) for i in range(3))
+    wq = (1 + 0.1 * rand((D if per_head else H * D,), torch.float32, 7)).to(torch.bfloat16)
+    wk = (1 + 0.1 * rand((D if per_head else H * D,), torch.float32, 8)).to(torch.bfloat16)
+    ang = rand((s, D // 2), torch.float32, 9) * 3
+    cos, sin = torch.cos(ang).repeat_interleave(2, 1).contiguous(), torch.sin(ang).repeat_interleave(2, 1).contiguous()
+    _check(ops, q, k, v, H, U, wq, wk, 1e-6, per_head, cos, sin, f"H{H} D{D} U{U} s{s}")
+
+
 def test_slices_of_a_fused_projection_and_optional_steps(ops):
     """q, k, v as column slices of one [B, s, 3*H*D] projection; norm or rotary embedding left out."""
     B, s, H, D = 1, 130, 12, 64

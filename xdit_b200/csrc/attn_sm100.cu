@@ -759,7 +759,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_sm100_kernel(const __gri
           if (a.acc_out) a.lse_acc[flat] = lse;
           else if (a.lse) a.lse[flat] = lse;
         }
-        if (!a.out && !a.acc_out) __threadfence_system();  // rows stored into peer GPUs' memory
       }
     }
   }
@@ -767,6 +766,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_sm100_kernel(const __gri
   // ---------------- teardown ----------------
   tc_fence_before();
   __syncthreads();
+  // Rows stored into peer GPUs' memory: one system-scope fence per CTA, after the barrier that
+  // orders every thread's stores before it.
+  if (threadIdx.x == 0 && !a.out && !a.acc_out) __threadfence_system();
   if (warp == 8) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");

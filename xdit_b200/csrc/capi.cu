@@ -93,9 +93,8 @@ static int pack_impl(const char* who, const struct xdit_pack_job* jobs, int32_t 
     return XDIT_E_SHAPE;
   }
   const int Hl = H / U;
-  const int npeer_jobs = peer_base ? U : 1;  // with per-peer bases every peer is a row-copy job of its own
-  if (peer_base && njobs * 2 * U > kMaxRowCopyJobs) {
-    set_error("%s: %d tensors x %d peers exceed the %d copy jobs of one launch", who, njobs, U, kMaxRowCopyJobs);
+  if (peer_base && U > kMaxRowCopyPeers) {
+    set_error("%s: U=%d peers (at most %d)", who, U, kMaxRowCopyPeers);
     return XDIT_E_SHAPE;
   }
   RowCopyJob rc[kMaxRowCopyJobs];
@@ -111,46 +110,39 @@ static int pack_impl(const char* who, const struct xdit_pack_job* jobs, int32_t 
       return XDIT_E_NULL;
     }
     const int64_t rows = (int64_t)pj.s + pj.s_joint;
-    // destination dims: (peer, head-in-peer, batch, row)
+    // destination dims: (peer, head-in-peer, batch, row); with per-peer bases the peer index picks
+    // the base and the job's destination is the offset inside every peer's buffer
     const int64_t d_row = (int64_t)D * es;
     const int64_t d_b = rows * d_row;
     const int64_t d_h = B * d_b;
-    const int64_t d_p = pj.dst_peer_stride * es;
+    const int64_t d_p = peer_base ? 0 : pj.dst_peer_stride * es;
     const int main_off = pj.joint_front ? pj.s_joint : 0;
     const int joint_off = pj.joint_front ? 0 : pj.s;
     const int64_t sp_main = (pj.src_stride_peer ? pj.src_stride_peer : (int64_t)Hl * pj.src_stride_h) * es;
     const int64_t sp_joint = (pj.joint_stride_peer ? pj.joint_stride_peer : (int64_t)Hl * pj.joint_stride_h) * es;
-    for (int pp = 0; pp < npeer_jobs; ++pp) {
-      char* dbase;
-      if (peer_base) {
-        if (!peer_base[pp]) { set_error("%s: NULL base pointer for peer %d", who, pp); return XDIT_E_NULL; }
-        dbase = (char*)peer_base[pp] + dst_offset[j] * es;
-      } else {
-        dbase = (char*)pj.dst;
-      }
-      if (pj.s) {
-        RowCopyJob& r = rc[n++];
-        r.src = (const char*)pj.src + (peer_base ? pp * sp_main : 0);
-        r.dst = dbase + main_off * d_row;
-        r.n[0] = peer_base ? 1 : U; r.n[1] = Hl; r.n[2] = B; r.n[3] = pj.s;
-        r.s_stride[0] = sp_main; r.s_stride[1] = pj.src_stride_h * es;
-        r.s_stride[2] = pj.src_stride_b * es; r.s_stride[3] = pj.src_stride_row * es;
-        r.d_stride[0] = d_p; r.d_stride[1] = d_h; r.d_stride[2] = d_b; r.d_stride[3] = d_row;
-        r.row_bytes = D * es;
-      }
-      if (pj.s_joint) {
-        RowCopyJob& r = rc[n++];
-        r.src = (const char*)pj.joint + (peer_base ? pp * sp_joint : 0);
-        r.dst = dbase + joint_off * d_row;
-        r.n[0] = peer_base ? 1 : U; r.n[1] = Hl; r.n[2] = B; r.n[3] = pj.s_joint;
-        r.s_stride[0] = sp_joint; r.s_stride[1] = pj.joint_stride_h * es;
-        r.s_stride[2] = pj.joint_stride_b * es; r.s_stride[3] = pj.joint_stride_row * es;
-        r.d_stride[0] = d_p; r.d_stride[1] = d_h; r.d_stride[2] = d_b; r.d_stride[3] = d_row;
-        r.row_bytes = D * es;
-      }
+    char* dbase = peer_base ? reinterpret_cast<char*>(static_cast<intptr_t>(dst_offset[j] * es)) : (char*)pj.dst;
+    if (pj.s) {
+      RowCopyJob& r = rc[n++];
+      r.src = (const char*)pj.src;
+      r.dst = dbase + main_off * d_row;
+      r.n[0] = U; r.n[1] = Hl; r.n[2] = B; r.n[3] = pj.s;
+      r.s_stride[0] = sp_main; r.s_stride[1] = pj.src_stride_h * es;
+      r.s_stride[2] = pj.src_stride_b * es; r.s_stride[3] = pj.src_stride_row * es;
+      r.d_stride[0] = d_p; r.d_stride[1] = d_h; r.d_stride[2] = d_b; r.d_stride[3] = d_row;
+      r.row_bytes = D * es;
+    }
+    if (pj.s_joint) {
+      RowCopyJob& r = rc[n++];
+      r.src = (const char*)pj.joint;
+      r.dst = dbase + joint_off * d_row;
+      r.n[0] = U; r.n[1] = Hl; r.n[2] = B; r.n[3] = pj.s_joint;
+      r.s_stride[0] = sp_joint; r.s_stride[1] = pj.joint_stride_h * es;
+      r.s_stride[2] = pj.joint_stride_b * es; r.s_stride[3] = pj.joint_stride_row * es;
+      r.d_stride[0] = d_p; r.d_stride[1] = d_h; r.d_stride[2] = d_b; r.d_stride[3] = d_row;
+      r.row_bytes = D * es;
     }
   }
-  return launch_row_copy(rc, n, (cudaStream_t)stream, peer_base != nullptr);
+  return launch_row_copy(rc, n, (cudaStream_t)stream, peer_base, peer_base ? U : 0);
 }
 }  // namespace xdit
 

@@ -41,9 +41,13 @@ struct RowCopyJob {
   int32_t n[4];
   int32_t row_bytes;
 };
-constexpr int kMaxRowCopyJobs = 36;  // 4 tensors (+ joint rows) x up to 8 peers
-// system_fence: the destinations may be peer GPUs' memory; every thread ends with a system-scope fence.
-int launch_row_copy(const RowCopyJob* jobs, int njobs, cudaStream_t stream, bool system_fence = false);
+constexpr int kMaxRowCopyJobs = 36;
+constexpr int kMaxRowCopyPeers = 16;
+// peer_base (npeers entries): index i0 of every job selects a base pointer, job.dst holds the byte
+// offset from that base and d_stride[0] is ignored; the destinations may then be peer GPUs' memory
+// and every thread ends with a system-scope fence.
+int launch_row_copy(const RowCopyJob* jobs, int njobs, cudaStream_t stream, void* const* peer_base = nullptr,
+                    int npeers = 0);
 
 // ---- attention kernels ------------------------------------------------------------------------
 // Argument check shared by the attention entry points (bounds B, H, D and the sequence lengths).

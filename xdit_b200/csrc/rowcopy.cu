@@ -24,7 +24,8 @@ struct RowCopyArgs {
   int64_t unit_end[kMaxRowCopyJobs];  // exclusive prefix end of each job's units
   int32_t blk1[kMaxRowCopyJobs];      // how many consecutive i1 a unit covers
   int32_t njobs;
-  int32_t system_fence;
+  int32_t npeers;  // > 0: index i0 selects peer[i0] and job.dst is a byte offset from that base
+  char* peer[kMaxRowCopyPeers];
 };
 
 template <int VEC>
@@ -56,8 +57,8 @@ __global__ void __launch_bounds__(kThreads) row_copy_kernel(const __grid_constan
     const bool zero = jb.src == nullptr;  // fill job (padding rows): nothing is read
     const char* s = jb.src + i0 * jb.s_stride[0] + i1 * jb.s_stride[1] + i2 * jb.s_stride[2] +
                     (int64_t)r0 * jb.s_stride[3];
-    char* d = jb.dst + i0 * jb.d_stride[0] + i1 * jb.d_stride[1] + i2 * jb.d_stride[2] +
-              (int64_t)r0 * jb.d_stride[3];
+    char* d = (args.npeers ? args.peer[i0] + reinterpret_cast<intptr_t>(jb.dst) : jb.dst + i0 * jb.d_stride[0]) +
+              i1 * jb.d_stride[1] + i2 * jb.d_stride[2] + (int64_t)r0 * jb.d_stride[3];
     const uint32_t vpr = jb.row_bytes / VEC;
     const uint32_t vpg = vpr * nhb;  // vectors per row group: nhb rows of adjacent i1
     const uint32_t nvec = nrows * vpg;
@@ -87,14 +88,17 @@ __global__ void __launch_bounds__(kThreads) row_copy_kernel(const __grid_constan
       *reinterpret_cast<V*>(d + dof) = zero ? V{} : __ldg(reinterpret_cast<const V*>(s + so));
     }
   }
-  if (args.system_fence) __threadfence_system();  // destinations in peer GPUs' memory
+  if (args.npeers) {  // destinations in peer GPUs' memory: one system-scope fence per CTA
+    __syncthreads();
+    if (threadIdx.x == 0) __threadfence_system();
+  }
 }
 
-int pick_vec(const RowCopyJob* jobs, int njobs) {
+int pick_vec(const RowCopyJob* jobs, int njobs, uint64_t base_bits) {
   int vec = 16;
   for (int j = 0; j < njobs; ++j) {
     uint64_t bits = (uint64_t)(uintptr_t)jobs[j].src | (uint64_t)(uintptr_t)jobs[j].dst |
-                    (uint64_t)jobs[j].row_bytes;
+                    (uint64_t)jobs[j].row_bytes | base_bits;
     for (int k = 0; k < 4; ++k) {
       if (jobs[j].n[k] > 1) bits |= (uint64_t)jobs[j].s_stride[k] | (uint64_t)jobs[j].d_stride[k];
     }
@@ -105,7 +109,7 @@ int pick_vec(const RowCopyJob* jobs, int njobs) {
 
 }  // namespace
 
-int launch_row_copy(const RowCopyJob* jobs, int njobs, cudaStream_t stream, bool system_fence) {
+int launch_row_copy(const RowCopyJob* jobs, int njobs, cudaStream_t stream, void* const* peer_base, int npeers) {
   if (njobs <= 0 || njobs > kMaxRowCopyJobs) {
     set_error("row copy: %d jobs (1..%d supported)", njobs, kMaxRowCopyJobs);
     return XDIT_E_SHAPE;
@@ -124,7 +128,7 @@ int launch_row_copy(const RowCopyJob* jobs, int njobs, cudaStream_t stream, bool
     int64_t units = (int64_t)jb.n[0] * ((jb.n[1] + hb - 1) / hb) * jb.n[2];
     units *= (jb.n[3] + kRowsPerUnit - 1) / kRowsPerUnit;
     if (units <= 0 || jb.row_bytes <= 0) continue;  // empty job: nothing to move
-    if (!jb.dst) {
+    if (!jb.dst && !peer_base) {
       set_error("row copy: NULL pointer in job %d", j);
       return XDIT_E_NULL;
     }
@@ -136,11 +140,24 @@ int launch_row_copy(const RowCopyJob* jobs, int njobs, cudaStream_t stream, bool
   }
   if (live == 0) return XDIT_OK;
   args.njobs = live;
-  args.system_fence = system_fence ? 1 : 0;
+  args.npeers = 0;
+  if (peer_base) {
+    if (npeers < 1 || npeers > kMaxRowCopyPeers) {
+      set_error("row copy: %d peer bases (1..%d supported)", npeers, kMaxRowCopyPeers);
+      return XDIT_E_SHAPE;
+    }
+    for (int q = 0; q < npeers; ++q) {
+      if (!peer_base[q]) { set_error("row copy: NULL base pointer for peer %d", q); return XDIT_E_NULL; }
+      args.peer[q] = (char*)peer_base[q];
+    }
+    args.npeers = npeers;
+  }
   int sms = 0;
   int rc = check_device(&sms);
   if (rc) return rc;
-  const int vec = pick_vec(args.job, live);
+  uint64_t base_bits = 0;
+  for (int q = 0; q < args.npeers; ++q) base_bits |= (uint64_t)(uintptr_t)args.peer[q];
+  const int vec = pick_vec(args.job, live, base_bits);
   int grid = (int)((total < (int64_t)sms * 8) ? total : (int64_t)sms * 8);
   if (grid < 1) grid = 1;
   switch (vec) {
