@@ -46,11 +46,10 @@ __device__ __forceinline__ void store_vec(T* p, const float (&in)[VEC]) {
   }
 }
 
-// One group of LPR lanes (a power of two, at most a warp) owns a row: its lanes stride over the row's
-// vectors, and the row's lse is rewritten only after every lane of the warp has read it
-// (__syncwarp).  A row never spans warps, so no other thread reads lse_acc[r].  A warp takes kRowsInFlight
-// row groups per iteration and issues all their loads before the arithmetic, which is what keeps enough
-// bytes in flight for an HBM-bound kernel.
+// One group of LPR lanes (a power of two, at most a warp) owns a row's vectors.  A row never spans warps,
+// so no other warp touches lse_acc[r].  A warp takes kRowsInFlight row groups per iteration and issues all
+// their loads before the arithmetic, which is what keeps enough bytes in flight for an HBM-bound kernel;
+// the per-row exponentials and logarithms are done once per row, by one lane, not by every lane of the row.
 constexpr int kRowsInFlight = 4;
 
 template <typename T, int VEC>
@@ -66,41 +65,46 @@ __global__ void __launch_bounds__(256) merge_kernel(float* __restrict__ o_acc, f
   const int64_t warp_id = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
   const int64_t n_groups = (rows + rows_per_warp - 1) / rows_per_warp;
-  const bool one_vec = vpr <= lpr;  // every lane has at most one vector of its row (D <= 128 with VEC 4)
+  // every lane has at most one vector of its row (D <= 128 with VEC 4) and an iteration's rows fit the lanes
+  const bool one_vec = vpr <= lpr && kRowsInFlight * rows_per_warp <= 32;
   for (int64_t g0 = warp_id * kRowsInFlight; g0 < n_groups; g0 += n_warps * kRowsInFlight) {
     if (one_vec) {
+      // The rows of one iteration are consecutive: row (g0 * rows_per_warp + L) belongs to lane L for the
+      // per-row arithmetic (lse, weight), one row per lane, and the weights are handed to the lanes that
+      // hold the row's vectors by shuffles.  No lane reads another row's lse from memory.
+      const int64_t row0 = g0 * rows_per_warp;
+      const bool has_row = lane < kRowsInFlight * rows_per_warp && row0 + lane < rows;
+      float la_l = 0.f, lb_l = 0.f;
+      if (has_row) {
+        lb_l = lse_b[row0 + lane];
+        if (!first) la_l = lse_acc[row0 + lane];
+      }
       int64_t r[kRowsInFlight];
-      bool live[kRowsInFlight];
-      float la[kRowsInFlight], lb[kRowsInFlight], ob[kRowsInFlight][VEC], oa[kRowsInFlight][VEC];
+      bool mine[kRowsInFlight];
+      float ob[kRowsInFlight][VEC], oa[kRowsInFlight][VEC];
 #pragma unroll
       for (int u = 0; u < kRowsInFlight; ++u) {
-        r[u] = (g0 + u) * rows_per_warp + lane / lpr;
-        live[u] = (g0 + u) < n_groups && r[u] < rows;
-        const bool mine = live[u] && sub < vpr;
-        la[u] = lb[u] = 0.f;
-        if (live[u]) {
-          lb[u] = lse_b[r[u]];
-          if (!first) la[u] = lse_acc[r[u]];
-        }
+        r[u] = row0 + u * rows_per_warp + lane / lpr;
+        mine[u] = r[u] < rows && sub < vpr;
 #pragma unroll
         for (int k = 0; k < VEC; ++k) ob[u][k] = oa[u][k] = 0.f;
-        if (mine) {
+        if (mine[u]) {
           const int64_t off = r[u] * D + (int64_t)sub * VEC;
           load_vec<T, VEC>(out_b + off, ob[u]);
           if (!first) load_vec<float, VEC>(o_acc + off, oa[u]);
         }
       }
-      __syncwarp();  // every lane has read its rows' lse before any of them is rewritten
+      float w_l = 0.f, lnew_l = lb_l;
+      if (!first && has_row) {
+        // both -inf (no keys seen on either side): keep the accumulator
+        if (la_l == -INFINITY && lb_l == -INFINITY) { w_l = 0.f; lnew_l = la_l; }
+        else { w_l = sigmoidf_(lb_l - la_l); lnew_l = la_l - logsigmoidf_(la_l - lb_l); }
+      }
+      if (has_row) lse_acc[row0 + lane] = lnew_l;
 #pragma unroll
       for (int u = 0; u < kRowsInFlight; ++u) {
-        if (!live[u]) continue;
-        float w = 0.f, lnew = lb[u];
-        if (!first) {
-          // both -inf (no keys seen on either side): keep the accumulator
-          if (la[u] == -INFINITY && lb[u] == -INFINITY) { w = 0.f; lnew = la[u]; }
-          else { w = sigmoidf_(lb[u] - la[u]); lnew = la[u] - logsigmoidf_(la[u] - lb[u]); }
-        }
-        if (sub < vpr) {
+        const float w = __shfl_sync(0xffffffffu, w_l, u * rows_per_warp + lane / lpr);
+        if (mine[u]) {
           const int64_t off = r[u] * D + (int64_t)sub * VEC;
           float res[VEC];
 #pragma unroll
@@ -108,7 +112,6 @@ __global__ void __launch_bounds__(256) merge_kernel(float* __restrict__ o_acc, f
           store_vec<float, VEC>(o_acc + off, res);
           if (out_final) store_vec<T, VEC>(out_final + off, res);
         }
-        if (sub == 0) lse_acc[r[u]] = lnew;
       }
     } else {
       // long rows (more vectors than lanes): one row group at a time, lanes stride over the row

@@ -18,6 +18,10 @@ constexpr int kRowsPerUnit = 64;
 constexpr int kThreads = 256;
 
 constexpr int kMaxBlock1 = 8;
+#ifndef XDIT_ROWCOPY_UNROLL
+#define XDIT_ROWCOPY_UNROLL 4
+#endif
+constexpr int kInFlight = XDIT_ROWCOPY_UNROLL;  // independent 16-byte loads per thread before the first store
 
 struct RowCopyArgs {
   RowCopyJob job[kMaxRowCopyJobs];
@@ -71,16 +75,16 @@ __global__ void __launch_bounds__(kThreads) row_copy_kernel(const __grid_constan
       dof = r * ds + h * ds1 + (int64_t)c * VEC;
     };
     uint32_t idx = threadIdx.x;
-    for (; idx + 3 * kThreads < nvec; idx += 4 * kThreads) {
-      V val[4];
-      int64_t so[4], dof[4];
+    for (; idx + (kInFlight - 1) * kThreads < nvec; idx += kInFlight * kThreads) {
+      V val[kInFlight];
+      int64_t so[kInFlight], dof[kInFlight];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
+      for (int k = 0; k < kInFlight; ++k) {
         locate(idx + k * kThreads, so[k], dof[k]);
         val[k] = zero ? V{} : __ldg(reinterpret_cast<const V*>(s + so[k]));
       }
 #pragma unroll
-      for (int k = 0; k < 4; ++k) *reinterpret_cast<V*>(d + dof[k]) = val[k];
+      for (int k = 0; k < kInFlight; ++k) *reinterpret_cast<V*>(d + dof[k]) = val[k];
     }
     for (; idx < nvec; idx += kThreads) {
       int64_t so, dof;
