@@ -194,8 +194,9 @@ XDIT_API int xdit_ulysses_pack(const struct xdit_pack_job* jobs, int32_t njobs, 
  * instead of into one local send buffer: peer_base[p] is rank p's receive buffer mapped into this
  * process (xdit_peer_open; the own rank's entry is a local pointer).  The send buffer, the NCCL
  * all-to-all and its receive copy (usp.py:87-108) collapse into one pass of plain peer stores over NVLink.
- * jobs[j].dst and dst_peer_stride are ignored.  The caller orders the readers on the other ranks after
- * this launch. */
+ * jobs[j].dst and dst_peer_stride are ignored; U is at most XDIT_MAX_PACK_PEERS.  The caller orders the
+ * readers on the other ranks after this launch. */
+#define XDIT_MAX_PACK_PEERS 16
 XDIT_API int xdit_ulysses_pack_peers(const struct xdit_pack_job* jobs, int32_t njobs, int32_t dtype, int32_t B,
                                      int32_t H, int32_t D, int32_t U, void* const* peer_base,
                                      const int64_t* dst_offset, void* stream);

@@ -42,7 +42,7 @@ struct RowCopyJob {
   int32_t row_bytes;
 };
 constexpr int kMaxRowCopyJobs = 36;
-constexpr int kMaxRowCopyPeers = 16;
+constexpr int kMaxRowCopyPeers = XDIT_MAX_PACK_PEERS;
 // peer_base (npeers entries): index i0 of every job selects a base pointer, job.dst holds the byte
 // offset from that base and d_stride[0] is ignored; the destinations may then be peer GPUs' memory
 // and every thread ends with a system-scope fence.
