@@ -452,10 +452,14 @@ def run_workload(torch, dist, xdit_b200, ops, name, w, args, device, rank, world
     inputs = make_layer_inputs(torch, w, P, rank, nsets, device)
     multi = world > 1
     exchange_note = None
-    if multi and U > 1 and R == 1:
+    if multi:
         exchange, exchange_note = choose_exchange(torch, dist, xdit_b200, ops, inputs, device, exchange)
+        if exchange == "peer_stores" and R > 1:
+            # ring legs: the K/V rotation by copy-engine transfers into the next rank's buffer; a Ulysses
+            # part in front of the ring (U > 1) stays on NCCL
+            exchange = "peer_copies"
     else:
-        exchange = "none" if P == 1 else "nccl"
+        exchange = "none"
 
     # correctness first: one call, sampled rows against the oracle
     out = xdit_b200.USP(*inputs[0])
@@ -554,7 +558,7 @@ def run_workload(torch, dist, xdit_b200, ops, name, w, args, device, rank, world
                       "host_gbs_per_rank": (bytes_in + bytes_out) / (ms_e / e2e_steps * 1e-3) / 1e9}
         del host, host_out, slots
     del inputs
-    if exchange == "peer_stores":
+    if exchange in ("peer_stores", "peer_copies"):
         from xdit_b200 import peer_exchange
 
         peer_exchange.enable(False)
@@ -1232,13 +1236,20 @@ def main():
             splits = [(1, world)] + ([(2, 4)] if world == 8 else []) + ([(2, 2)] if world == 4 else [])
             for (u, r) in splits:
                 extra[f"wan_ring_u{u}r{r}"], ok = leg(torch, dist, xdit_b200, ops, "wan", WORKLOADS["wan"], args,
-                                                      device, rank, world, 4, u, r, tf_peak, steps=2)
+                                                      device, rank, world, 4, u, r, tf_peak, steps=2,
+                                                      exchange=args.exchange)
                 all_ok &= ok
+                if extra[f"wan_ring_u{u}r{r}"].get("exchange") == "peer_copies":
+                    # the same split with the rotation over NCCL send/recv
+                    extra[f"wan_ring_u{u}r{r}_nccl"], ok = leg(torch, dist, xdit_b200, ops, "wan", WORKLOADS["wan"],
+                                                               args, device, rank, world, 4, u, r, tf_peak, steps=2,
+                                                               exchange="nccl")
+                    all_ok &= ok
         # the ring-dominant long-context case (119,056 tokens); ring degree = ranks, one GPU runs it dense
         wh = WORKLOADS["hunyuan"]
         if wh["S"] % world == 0 and want("hunyuan"):
             extra["hunyuan_ring"], ok = leg(torch, dist, xdit_b200, ops, "hunyuan", wh, args, device, rank, world,
-                                            2, 1, world, tf_peak, steps=2)
+                                            2, 1, world, tf_peak, steps=2, exchange=args.exchange)
             all_ok &= ok
         if world % 4 == 0 and want("pp"):
             try:

@@ -223,6 +223,14 @@ XDIT_API int xdit_peer_free(void* ptr);
 XDIT_API int xdit_peer_barrier(void* const* peer_flags, void* local_flags, void* epoch, int32_t U, int32_t rank,
                                uint32_t wait_limit_ns, int32_t* status, int32_t* status_host, void* stream);
 
+/* One asynchronous copy of `bytes` bytes from this GPU's memory into a buffer that may be a peer's
+ * (xdit_peer_open), issued on `stream` as a single cudaMemcpyAsync: the copy engines move it over NVLink
+ * and no SM is used.  The ring K/V rotation uses it in place of an NCCL send/recv pair
+ * (usp.py:46-74 via torch's ring rotater; ring_flash_attn.py:84-87,140-143), whose kernels would hold SMs
+ * that the attention kernel, with one CTA per SM, then has to do without.  The caller orders the readers
+ * with xdit_peer_barrier after the copy. */
+XDIT_API int xdit_peer_copy(void* dst, const void* src, int64_t bytes, void* stream);
+
 /* Ulysses output pack in the reference's own wire layout: [B,Hl,S,D] (any strides) ->
  * send buffer [S][B][Hl][D] contiguous (peer p's block = rows [p*S/U,(p+1)*S/U)), and the
  * inverse on the receive side: [U][s][B][Hl][D] -> [B][U*Hl][s][D] contiguous.

@@ -44,7 +44,8 @@ def test_reference_layer_on_the_shim_multi_gpu(world, dtype, tol):
 @pytest.mark.parametrize("mode,dtype,tol", [("usp", "float32", 5e-5), ("usp", "bfloat16", 2e-2),
                                             ("legacy", "bfloat16", 2e-2), ("compat", "float32", 5e-5),
                                             ("yunchang", "bfloat16", 2e-2), ("usp_pipelined", "bfloat16", 2e-2),
-                                            ("usp_pipelined", "float32", 5e-5), ("usp_peer", "bfloat16", 2e-2)])
+                                            ("usp_pipelined", "float32", 5e-5), ("usp_peer", "bfloat16", 2e-2),
+                                            ("usp_peer", "float32", 5e-5)])
 def test_two_gpus(mode, dtype, tol):
     _need(2)
     run(2, golden_files(2), mode, 29750, backend="nccl", dtype_name=dtype, tol=tol)
@@ -52,7 +53,7 @@ def test_two_gpus(mode, dtype, tol):
 
 @pytest.mark.parametrize("mode,dtype,tol", [("usp", "float32", 5e-5), ("usp", "bfloat16", 2e-2),
                                             ("yunchang", "float32", 5e-5), ("usp_pipelined", "bfloat16", 2e-2),
-                                            ("usp_peer", "bfloat16", 2e-2)])
+                                            ("usp_peer", "bfloat16", 2e-2), ("usp_peer", "float32", 5e-5)])
 def test_four_gpus(mode, dtype, tol):
     _need(4)
     run(4, golden_files(4), mode, 29760, backend="nccl", dtype_name=dtype, tol=tol)

@@ -49,7 +49,8 @@ def worker(rank, world, port, files, mode, errq, backend="gloo", dtype_name="flo
                 kw = dict(joint_query=put(z["jq"]), joint_key=put(z["jk"]), joint_value=put(z["jv"]),
                           joint_strategy=strat)
             if mode == "usp_peer":
-                # both Ulysses exchanges by direct stores into the peers' buffers (CUDA IPC mappings)
+                # both Ulysses exchanges by direct stores into the peers' buffers (CUDA IPC mappings); ring
+                # fixtures rotate K/V by copy-engine transfers into the next rank's buffer
                 from xdit_b200 import peer_exchange
 
                 peer_exchange.enable(True)

@@ -32,6 +32,7 @@ EXPORTS = [
     "xdit_peer_close",
     "xdit_peer_free",
     "xdit_peer_barrier",
+    "xdit_peer_copy",
     "xdit_ulysses_pack_out",
     "xdit_ulysses_unpack_out",
     "xdit_ulysses_unpack_in",
@@ -154,6 +155,8 @@ def load() -> C.CDLL:
     lib.xdit_peer_barrier.argtypes = [C.POINTER(C.c_void_p), C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_uint32,
                                       C.c_void_p, C.c_void_p, C.c_void_p]
     lib.xdit_peer_barrier.restype = C.c_int
+    lib.xdit_peer_copy.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]
+    lib.xdit_peer_copy.restype = C.c_int
     lib.xdit_ulysses_pack_out.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p,
                                           C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]
     lib.xdit_ulysses_pack_out.restype = C.c_int

@@ -200,6 +200,15 @@ int xdit_peer_free(void* ptr) {
   return XDIT_OK;
 }
 
+int xdit_peer_copy(void* dst, const void* src, int64_t bytes, void* stream) {
+  if (!dst || !src) { set_error("xdit_peer_copy: NULL pointer"); return XDIT_E_NULL; }
+  if (bytes < 0) { set_error("xdit_peer_copy: bytes=%lld", (long long)bytes); return XDIT_E_SHAPE; }
+  if (bytes == 0) return XDIT_OK;
+  cudaError_t e = cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyDeviceToDevice, (cudaStream_t)stream);
+  if (e != cudaSuccess) return cuda_fail(e, "xdit_peer_copy: cudaMemcpyAsync");
+  return XDIT_OK;
+}
+
 int xdit_qk_norm_rope_pack(const struct xdit_prologue_params* p, void* stream) {
   if (!p) { set_error("xdit_qk_norm_rope_pack: NULL params"); return XDIT_E_NULL; }
   if (p->dtype != XDIT_BF16 && p->dtype != XDIT_F16) {

@@ -368,6 +368,17 @@ def peer_barrier(peer_flags: Sequence[int], local_flags: int, epoch: torch.Tenso
     launch_count += 1
 
 
+def peer_copy(dst_ptr: int, src: torch.Tensor, nbytes: int) -> None:
+    """One copy-engine transfer of the first ``nbytes`` bytes of ``src`` (contiguous, on this GPU) to the device
+    address ``dst_ptr`` -- possibly a peer's buffer (``peer_open``) -- on the current stream (``xdit_peer_copy``)."""
+    _require_cuda(src)
+    if not src.is_contiguous() or nbytes > src.numel() * src.element_size():
+        raise ValueError("peer_copy needs a contiguous source of at least nbytes bytes")
+    with torch.cuda.device(src.device):
+        _capi.check(_capi.load().xdit_peer_copy(C.c_void_p(int(dst_ptr)), C.c_void_p(src.data_ptr()), int(nbytes),
+                                                _stream(src)), "xdit_peer_copy")
+
+
 def ulysses_pack_out(x: torch.Tensor) -> torch.Tensor:
     """[B,Hl,S,D] -> [S,B,Hl,D] contiguous (the reference's output-side wire layout)."""
     global launch_count

@@ -34,16 +34,23 @@ import torch.distributed as dist
 from . import ops
 
 _ENABLED = False
+_RING = False
 _MIN_BYTES = 0
 _MAX_BYTES = 1 << 62
 _exchanges: Dict[int, "PeerExchange"] = {}
 
 
-def enable(on: bool = True, min_bytes: int = 0, max_bytes: int = 1 << 62) -> None:
+def enable(on: bool = True, min_bytes: int = 0, max_bytes: int = 1 << 62, ring: Optional[bool] = None) -> None:
     """Switch the direct-store exchange on for Ulysses-only calls whose per-rank send volume lies in
-    ``[min_bytes, max_bytes]`` (other calls keep the NCCL path)."""
-    global _ENABLED, _MIN_BYTES, _MAX_BYTES
+    ``[min_bytes, max_bytes]`` (other calls keep the NCCL path).  ``ring`` (default: the same as ``on``)
+    switches the ring K/V rotation from NCCL send/recv to copy-engine transfers into the next rank's buffer."""
+    global _ENABLED, _RING, _MIN_BYTES, _MAX_BYTES
     _ENABLED, _MIN_BYTES, _MAX_BYTES = bool(on), int(min_bytes), int(max_bytes)
+    _RING = bool(on) if ring is None else bool(ring)
+
+
+def ring_enabled() -> bool:
+    return _RING
 
 
 def enabled_for(nbytes: int) -> bool:

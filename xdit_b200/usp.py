@@ -184,6 +184,12 @@ def _ring_native(q, kv_buf, kv_views, joint_k, joint_v, front, out, group, scale
     sq = q.shape[2] if q.dim() == 4 else q.shape[2] * q.shape[3]
     o_acc = torch.empty(B, Hl, sq, D, dtype=torch.float32, device=q.device)
     lse_acc = torch.empty(B, Hl, sq, dtype=torch.float32, device=q.device)
+    if q.is_cuda and not causal and kv_buf.is_contiguous():
+        from . import peer_exchange
+
+        if peer_exchange.ring_enabled():
+            return _ring_peer_copies(q, kv_buf, kv_views, joint_k, joint_v, front, out, group, scale, lse, o_acc,
+                                     lse_acc)
     cur = kv_buf
     spare = torch.empty_like(kv_buf)
     # with a causal mask the shard of step i is visible only when i <= rank, and only step 0
@@ -207,6 +213,43 @@ def _ring_native(q, kv_buf, kv_views, joint_k, joint_v, front, out, group, scale
             for r in reqs:
                 r.wait()
             cur, spare = spare, cur
+    return out
+
+
+def _ring_peer_copies(q, kv_buf, kv_views, joint_k, joint_v, front, out, group, scale, lse, o_acc, lse_acc):
+    """The same ring with the K/V rotation done by the copy engines: at step i this rank's current block is
+    copied into the next rank's spare slot (one ``cudaMemcpyAsync`` to peer-mapped memory on a side stream,
+    ``xdit_peer_copy``) while the attention kernel, which wants every SM, works on it; the ranks meet in
+    ``xdit_peer_barrier`` between steps.  NCCL's send/recv kernels are not involved, so no SM is taken from the
+    attention kernel.  Slot (i+1) % 2 of the next rank is free at step i: that rank read it at step i-1 (and
+    copied it on), and the barrier after step i-1 has passed; the barrier at the start covers the previous
+    call's last reads."""
+    from . import peer_exchange
+
+    R = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    nbytes = kv_buf.numel() * kv_buf.element_size()
+    ex = peer_exchange.get(group, 256, nbytes, q.device)
+    nxt = (rank + 1) % R
+    ts = _TwoStreams(q.device)
+    ts.keep_for_side([kv_buf])
+    ex.sync()
+    cur = kv_buf
+    for i in range(R):
+        if i < R - 1:
+            ts.side_waits_cur()  # the barrier that ended step i-1 (or opened the call) lies behind
+            with ts.on(1):
+                ops.peer_copy(ex.out_peers((i + 1) % 2)[nxt], cur, nbytes)
+        k_i, v_i = kv_views(cur)
+        use_joint = joint_k is not None and ((front and i == 0) or ((not front) and i == R - 1))
+        last = i == R - 1
+        ops.attn_fwd(q, k_i, v_i, joint_k if use_joint else None, joint_v if use_joint else None,
+                     out=out if last else None, lse=lse if last else None, o_acc=o_acc, lse_acc=lse_acc,
+                     acc_in=i > 0, acc_out=not last, scale=scale)
+        if i < R - 1:
+            ts.cur_waits_side()
+            ex.sync()
+            cur = ex.out_local((i + 1) % 2, kv_buf.dtype)[:kv_buf.numel()]
     return out
 
 
