@@ -607,7 +607,8 @@ def usp_native(query, key, value, joint_query, joint_key, joint_value, joint_str
 
         def kv_views(buf, kv_stride=kv_stride, k_off=k_off):
             shape, strides = (B, Hl, U, sk, D), (sk * D, B * sk * D, kv_stride, D, 1)
-            return buf.as_strided(shape, strides, k_off), buf.as_strided(shape, strides, k_off + kv_blk)
+            base = buf.storage_offset() + k_off  # as_strided counts from the storage, and buf may be a slice
+            return buf.as_strided(shape, strides, base), buf.as_strided(shape, strides, base + kv_blk)
 
         q_att = q5
         k_att, v_att = kv_views(kv_recv)
