@@ -88,3 +88,24 @@ def test_flux_joint_fp32_case_at_full_size_two_ranks():
     """Ulysses 2, 24 heads x 128, 4096 image + 512 joint text tokens (rear), fp32, seed 0: the host logic at
     the full shape (the stand-in attention is torch's fp32 CPU kernel here; the float64 oracle checks it)."""
     run_flux_joint(2, 29761, tol=2e-5)
+
+
+def test_kv_views_over_a_slot_of_a_larger_buffer():
+    """The ring hands the view builder a slice of a peer-mapped buffer (slot 0 or 1): the views must address
+    the slice, not the start of the storage it lives in."""
+    import torch
+
+    from xdit_b200.usp import _segmented_kv_views
+
+    B, Hl, U, sk, D = 1, 2, 2, 5, 8
+    kv_blk = Hl * B * sk * D
+    stride = 2 * kv_blk
+    flat = torch.arange(U * stride, dtype=torch.float32)
+    k0, v0 = _segmented_kv_views(flat, B, Hl, U, sk, D, stride, 0, kv_blk)
+    big = torch.full((3 * flat.numel() + 7,), -1.0)
+    for off in (0, 7, flat.numel() + 7):
+        slot = big[off:off + flat.numel()]
+        slot.copy_(flat)
+        k1, v1 = _segmented_kv_views(slot, B, Hl, U, sk, D, stride, 0, kv_blk)
+        assert torch.equal(k1, k0) and torch.equal(v1, v0), off
+        slot.fill_(-1.0)

@@ -253,6 +253,15 @@ def _ring_peer_copies(q, kv_buf, kv_views, joint_k, joint_v, front, out, group, 
     return out
 
 
+def _segmented_kv_views(buf, B, Hl, U, sk, D, kv_stride, k_off, kv_blk):
+    """K and V as ``[B, Hl, U, sk, D]`` views of a flat exchange buffer whose U blocks lie ``kv_stride``
+    elements apart, K at ``k_off`` and V ``kv_blk`` elements behind it inside a block.  ``buf`` may itself be
+    a slice of a larger buffer (a ring slot): ``as_strided`` counts its offset from the start of the storage."""
+    shape, strides = (B, Hl, U, sk, D), (sk * D, B * sk * D, kv_stride, D, 1)
+    base = buf.storage_offset() + k_off
+    return buf.as_strided(shape, strides, base), buf.as_strided(shape, strides, base + kv_blk)
+
+
 def _pack_kv_flat(k, v):
     """Copy (possibly strided) k, v [B,H,S,D] into one flat buffer [k | v], each [B,H,S,D] contiguous."""
     B, H, S, D = k.shape
@@ -606,9 +615,7 @@ def usp_native(query, key, value, joint_query, joint_key, joint_value, joint_str
             kv_stride, k_off = 2 * kv_blk, 0
 
         def kv_views(buf, kv_stride=kv_stride, k_off=k_off):
-            shape, strides = (B, Hl, U, sk, D), (sk * D, B * sk * D, kv_stride, D, 1)
-            base = buf.storage_offset() + k_off  # as_strided counts from the storage, and buf may be a slice
-            return buf.as_strided(shape, strides, base), buf.as_strided(shape, strides, base + kv_blk)
+            return _segmented_kv_views(buf, B, Hl, U, sk, D, kv_stride, k_off, kv_blk)
 
         q_att = q5
         k_att, v_att = kv_views(kv_recv)
