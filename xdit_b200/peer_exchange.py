@@ -12,8 +12,8 @@ the two kernels that already touch every byte can do the moving themselves:
   collective and the head-merge re-layout in front of the output projection are gone, and the transfer
   overlaps the arithmetic tile by tile.
 
-Only plain stores to peer-mapped memory are used (no multicast, no loads from peers, no library kernel is
-handed a peer pointer); every kernel reads local memory only.  After each of the two kernels the ranks meet
+Only plain stores to peer-mapped memory are used (no broadcast forms, no loads from peers, no library
+kernel is handed a peer pointer); every kernel reads local memory only.  After each of the two kernels the ranks meet
 in ``xdit_peer_barrier``: one warp per rank stores the rank's barrier count into every peer's flag array
 and waits, with a time limit, until all counts have arrived in its own (a few microseconds; a one-element
 NCCL all-reduce in the same place measured tens).  A wait that runs out sets the device's attention status
