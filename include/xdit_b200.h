@@ -129,9 +129,19 @@ struct xdit_attn_params {
    * consumers on the other ranks after this launch (a collective or an event).  At most
    * XDIT_MAX_OUT_SEGMENTS segments; served by the tcgen05 kernel only (XDIT_E_DTYPE otherwise). */
   void* const* out_segments;
+  /* Optional scratch that lets the tcgen05 kernel split the keys of a call over several CTAs per pair of
+   * query tiles when the launch would otherwise fill at most half of the GPU's SMs (a Flux layer at Ulysses
+   * degree 8 is 54 CTAs): every split writes a normalised fp32 partial result and its log-sum-exp here and a
+   * second, small kernel merges them into the output (same formula as the ring merge).  Device memory,
+   * 16-byte aligned, of split_scratch_bytes bytes; NULL / 0: never split.  Not used together with acc_in /
+   * acc_out.  xdit_attn_split_scratch_bytes() gives the size that allows every split the library would
+   * choose for a parameter block (0 when it would not split). */
+  void* split_scratch;
+  int64_t split_scratch_bytes;
 };
 #define XDIT_MAX_OUT_SEGMENTS 16
 XDIT_API int xdit_attn_fwd(const struct xdit_attn_params* p, void* stream);
+XDIT_API int64_t xdit_attn_split_scratch_bytes(const struct xdit_attn_params* p);
 /* Which kernel xdit_attn_fwd would run for these parameters: 1 = tcgen05/TMEM/TMA kernel,
  * 0 = CUDA-core kernel, negative = the error the call would return. */
 XDIT_API int xdit_attn_which(const struct xdit_attn_params* p);

@@ -364,12 +364,13 @@ def test_launch_after_a_failure_is_a_no_op_until_cleared(ops):
     compare(out, oracle_attn(q, k, v)[0], "after clearing")
 
 
+@pytest.mark.parametrize("Sk", [500, 2100])  # 2100 keys: the launch splits its keys and the merge kernel stores the rows
 @pytest.mark.parametrize("D", [128, 64])
-def test_segment_outputs_to_separate_bases(ops, D):
+def test_segment_outputs_to_separate_bases(ops, D, Sk):
     """out_segments: the rows of query segment g go to a base address of their own, laid out
     [B, rows, H_total, D] with this call's heads at a column offset -- what the epilogue does when it stores
     every source rank's rows into that rank's result buffer.  Must equal the ordinary output bit for bit."""
-    B, Hl, G, L, Sk, Htot, hoff = 1, 3, 4, 200, 500, 12, 6
+    B, Hl, G, L, Htot, hoff = 1, 3, 4, 200, 12, 6
     q = rand((B, Hl, G, L, D), torch.bfloat16, 60)
     k, v = rand((B, Hl, Sk, D), torch.bfloat16, 61), rand((B, Hl, Sk, D), torch.bfloat16, 62)
     want, _ = _run(ops, q, k, v)  # [B, Hl, G, L, D]
@@ -386,3 +387,34 @@ def test_segment_outputs_to_separate_bases(ops, D):
 
     with pytest.raises(_capi.XditError):  # the CUDA-core kernel does not serve it
         ops.attn_fwd(q.float(), k.float(), v.float(), out_segments=segs, out_strides=(L * Htot * D, D, Htot * D))
+
+
+@pytest.mark.parametrize("H,Sq,Sk,Sj,D,G", [(2, 1000, 2100, 0, 128, 1), (3, 300, 1537, 77, 128, 1),
+                                             (2, 512, 4096, 0, 72, 1), (1, 256, 1100, 50, 64, 1),
+                                             (2, 200, 2048, 0, 128, 3), (3, 4608, 4608, 0, 128, 1)])
+def test_keys_split_over_ctas_equals_unsplit(ops, H, Sq, Sk, Sj, D, G):
+    """A launch that would fill at most half of the SMs splits its keys over several CTAs per pair of query
+    tiles and merges the partial results in a second kernel (the last case is a Flux layer's shard at Ulysses
+    degree 8).  Same result as the unsplit kernel up to the rounding of the merge, same log-sum-exp, joint
+    second source, ragged lengths, head_dim 64 / 72 and segmented queries included."""
+    B = 1
+    q = rand((B, H, G, Sq, D) if G > 1 else (B, H, Sq, D), torch.bfloat16, 70)
+    k, v = rand((B, H, Sk, D), torch.bfloat16, 71), rand((B, H, Sk, D), torch.bfloat16, 72)
+    k2 = v2 = None
+    if Sj:
+        k2, v2 = rand((B, H, Sj, D), torch.bfloat16, 73), rand((B, H, Sj, D), torch.bfloat16, 74)
+    assert ops.attn_split_scratch_bytes(q, k, v, k2, v2) > 0
+    try:
+        ops.SPLIT_KEYS = False
+        out0, lse0 = _run(ops, q, k, v, k2, v2)
+    finally:
+        ops.SPLIT_KEYS = True
+    out1, lse1 = _run(ops, q, k, v, k2, v2)
+    assert float((out1.float() - out0.float()).abs().max()) <= 8e-3
+    assert float((lse1 - lse0).abs().max()) <= 1e-4
+    if Sq * Sk <= 4_000_000:
+        kk = k if k2 is None else torch.cat([k, k2], 2)
+        vv = v if v2 is None else torch.cat([v, v2], 2)
+        want, want_lse = oracle_attn(q.reshape(B, H, -1, D), kk, vv)
+        compare(out1.reshape(B, H, -1, D), want, "out")
+        compare(lse1.reshape(B, H, -1), want_lse, "lse", max_abs=2e-3, cos=0.0)

@@ -23,6 +23,7 @@ EXPORTS = [
     "xdit_query_caps",
     "xdit_last_error_string",
     "xdit_attn_fwd",
+    "xdit_attn_split_scratch_bytes",
     "xdit_attn_which",
     "xdit_attn_fwd_static_acc",
     "xdit_ulysses_pack",
@@ -72,6 +73,8 @@ class AttnParams(C.Structure):
         ("status", C.c_void_p),
         ("status_host", C.c_void_p), ("wait_limit_ns", C.c_uint32), ("selftest_stall", C.c_int32),
         ("out_segments", C.POINTER(C.c_void_p)),
+        ("split_scratch", C.c_void_p),
+        ("split_scratch_bytes", C.c_int64),
     ]
 
 
@@ -133,6 +136,8 @@ def load() -> C.CDLL:
     lib.xdit_last_error_string.restype = C.c_char_p
     lib.xdit_attn_fwd.argtypes = [C.POINTER(AttnParams), C.c_void_p]
     lib.xdit_attn_fwd.restype = C.c_int
+    lib.xdit_attn_split_scratch_bytes.argtypes = [C.POINTER(AttnParams)]
+    lib.xdit_attn_split_scratch_bytes.restype = C.c_int64
     lib.xdit_attn_fwd_static_acc.argtypes = [C.POINTER(AttnParams), C.c_void_p]
     lib.xdit_attn_fwd_static_acc.restype = C.c_int
     lib.xdit_attn_which.argtypes = [C.POINTER(AttnParams)]

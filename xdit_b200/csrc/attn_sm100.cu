@@ -67,6 +67,12 @@ struct alignas(64) Sm100Args {
   int32_t* status_host;     // optional pinned host word (mapped): written on a timeout only, never read
   uint32_t wait_limit_ns;   // time limit of every mbarrier wait
   int32_t selftest_stall;   // test aid: the loader leaves K/V stage 0 un-armed, so a consumer's wait runs out
+  // keys split over kv_splits CTAs per pair of query tiles (blockIdx.x = split * pairs + pair); every split
+  // writes a normalised fp32 partial result [kv_splits][part_rows][D] and its log-sum-exp [kv_splits][part_rows]
+  int32_t kv_splits, pairs;
+  int64_t part_rows;
+  float* part_o;
+  float* part_lse;
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -350,8 +356,10 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_sm100_kernel(const __gri
   volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + L::kMiscOff + 4);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int pair = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-  const int n_tiles = a.n_kv_tiles;
+  const int split = blockIdx.x / a.pairs, pair = blockIdx.x - split * a.pairs, h = blockIdx.y, b = blockIdx.z;
+  // key tiles [jt0, jt0 + n_tiles) of the a.n_kv_tiles belong to this CTA (all of them without a split)
+  const int jt0 = (int)((int64_t)split * a.n_kv_tiles / a.kv_splits);
+  const int n_tiles = (int)((int64_t)(split + 1) * a.n_kv_tiles / a.kv_splits) - jt0;
   // query tile t of this CTA covers query chunks 4*pair + 2t and 4*pair + 2t + 1
   const bool tile_on[2] = {4 * pair < a.q_chunks, 4 * pair + 2 < a.q_chunks};
 
@@ -416,7 +424,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_sm100_kernel(const __gri
         const int j = i >> 1;
         const bool is_v = i & 1;
         for (int c = 0; c < 2; ++c) {
-          const ChunkLoc loc = kv_chunk(a, 2 * j + c);
+          const ChunkLoc loc = kv_chunk(a, 2 * (jt0 + j) + c);
           const CUtensorMap* tm = loc.src ? (is_v ? &a.tm_v2 : &a.tm_k2) : (is_v ? &a.tm_v : &a.tm_k);
           for (int s = 0; s < SLABS; ++s)
             tma_load_5d(kv_smem + stage * L::kStageBytes + s * kSlabBytes + c * kBoxBytes, tm, bar_kv_full(stage),
@@ -560,7 +568,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_sm100_kernel(const __gri
     float l_run = 0.f;
     const float sl2 = a.scale_log2;
     // valid key columns of the next chunk, tracked without divisions
-    int cidx = 0, cpos = 0;
+    int cidx = 2 * jt0, cpos = (2 * jt0 < a.k_chunks_main) ? (2 * jt0) % a.k_cps : 0;
     auto next_valid = [&]() -> int {
       int v;
       if (cidx < a.k_chunks_main) {
@@ -713,6 +721,27 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_sm100_kernel(const __gri
             lse = la - (fminf(y, 0.f) - log1pf(__expf(-fabsf(y))));
           }
         }
+        if (a.kv_splits > 1) {
+          // partial result of this CTA's share of the keys: normalised fp32 rows and their log-sum-exp; the
+          // merge kernel that follows on the stream writes the output
+          float* prow = a.part_o + ((int64_t)split * a.part_rows + flat) * a.D;
+          for (int c0 = 0; c0 < a.dv_n; c0 += 32) {
+            uint32_t o[32];
+            XDIT_TMEM_LD32(o, 0, tmem_o + c0);
+            tmem_wait_ld();
+            if (live) {
+#pragma unroll
+              for (int g = 0; g < 8; ++g) {
+                const int col = c0 + 4 * g;
+                if (col < a.D)
+                  *reinterpret_cast<float4*>(prow + col) =
+                      make_float4(__uint_as_float(o[4 * g]) * inv_l, __uint_as_float(o[4 * g + 1]) * inv_l,
+                                  __uint_as_float(o[4 * g + 2]) * inv_l, __uint_as_float(o[4 * g + 3]) * inv_l);
+              }
+            }
+          }
+          if (live) a.part_lse[(int64_t)split * a.part_rows + flat] = lse;
+        } else {
         unsigned char* orow = nullptr;
         if (!a.acc_out) {
           // one base per query segment when the rows go to their source ranks' buffers, else one tensor
@@ -758,6 +787,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_sm100_kernel(const __gri
         if (live) {
           if (a.acc_out) a.lse_acc[flat] = lse;
           else if (a.lse) a.lse[flat] = lse;
+        }
         }
       }
     }
@@ -893,6 +923,68 @@ bool seq_ok(const xdit_seq& s, int B, int H, int D, const char* name) {
   return true;
 }
 
+// Merge of the key splits' partial results into the output: one warp per query row, lane l owns columns
+// 4l..4l+3.  out = sum_s w_s O_s / sum_s w_s with w_s = exp(lse_s - max lse), the log-sum-exp of the whole
+// row is max + log(sum w): the formula of the ring merge for any number of partials.
+template <bool BF16>
+__global__ void __launch_bounds__(256) split_merge_kernel(const __grid_constant__ Sm100Args a) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (int64_t row = warp0; row < a.part_rows; row += nwarps) {
+    float ls[4], m = -INFINITY;
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+      ls[s] = s < a.kv_splits ? a.part_lse[(int64_t)s * a.part_rows + row] : -INFINITY;
+      m = fmaxf(m, ls[s]);
+    }
+    float wsum = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
+    const int col = 4 * lane;
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+      if (s < a.kv_splits) {
+        const float w = __expf(ls[s] - m);
+        wsum += w;
+        if (col < a.D) {
+          const float4 o = *reinterpret_cast<const float4*>(a.part_o + ((int64_t)s * a.part_rows + row) * a.D + col);
+          acc[0] = fmaf(w, o.x, acc[0]); acc[1] = fmaf(w, o.y, acc[1]);
+          acc[2] = fmaf(w, o.z, acc[2]); acc[3] = fmaf(w, o.w, acc[3]);
+        }
+      }
+    }
+    const float inv = 1.f / wsum;
+    const int64_t bh = row / a.sq_total;
+    const int rs = (int)(row - bh * a.sq_total);
+    const int b = (int)(bh / a.H), h = (int)(bh - (int64_t)b * a.H);
+    const int seg = rs / a.q_seg_len, trow = rs - seg * a.q_seg_len;
+    if (col < a.D) {
+      unsigned char* obase = a.out ? reinterpret_cast<unsigned char*>(a.out) + 2 * seg * a.out_stride_seg
+                                   : reinterpret_cast<unsigned char*>(a.out_seg[seg]);
+      unsigned char* orow = obase + 2 * (b * a.out_stride_b + h * a.out_stride_h + trow * a.out_stride_row);
+      uint2 pk;
+      pk.x = pack2<BF16>(acc[0] * inv, acc[1] * inv);
+      pk.y = pack2<BF16>(acc[2] * inv, acc[3] * inv);
+      *reinterpret_cast<uint2*>(orow + 2 * col) = pk;
+    }
+    if (lane == 0 && a.lse) a.lse[row] = m + __logf(wsum);
+  }
+  if (!a.out) {  // rows stored into peer GPUs' memory: one system-scope fence per CTA
+    __syncthreads();
+    if (threadIdx.x == 0) __threadfence_system();
+  }
+}
+
+// How many CTAs per pair of query tiles the keys of a call are split over: as many as fit the GPU's SMs
+// beside each other, at most 4, every split at least 4 key tiles long, and only what the scratch can hold.
+int choose_kv_splits(const xdit_attn_params& p, int sms, int n_kv_tiles, int ctas, int64_t part_rows, int64_t scratch_bytes) {
+  if (p.acc_in || p.acc_out || ctas <= 0) return 1;
+  int want = sms / ctas;
+  if (want > 4) want = 4;
+  if (want > n_kv_tiles / 4) want = n_kv_tiles / 4;
+  while (want > 1 && scratch_bytes >= 0 && (int64_t)want * part_rows * (p.D + 1) * 4 > scratch_bytes) --want;
+  return want < 2 ? 1 : want;
+}
+
 template <int SLABS, int NSTAGE, bool BF16>
 int launch_inst(const Sm100Args& a, dim3 grid, cudaStream_t stream) {
   using L = SmemLayout<SLABS, NSTAGE>;
@@ -914,6 +1006,16 @@ int launch_inst(const Sm100Args& a, dim3 grid, cudaStream_t stream) {
   attn_fwd_sm100_kernel<SLABS, NSTAGE, BF16><<<grid, kThreads, L::kDynamic, stream>>>(a);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "attn_fwd_sm100_kernel launch");
+  if (a.kv_splits > 1) {
+    // a few CTAs per SM striding over the rows: with per-segment bases every CTA ends with a system fence
+    int sms = 0;
+    if (check_device(&sms) != XDIT_OK || sms <= 0) sms = 148;
+    int64_t blocks = (a.part_rows * 32 + 255) / 256;
+    if (blocks > (int64_t)sms * 4) blocks = (int64_t)sms * 4;
+    split_merge_kernel<BF16><<<(int)blocks, 256, 0, stream>>>(a);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "split_merge_kernel launch");
+  }
   return XDIT_OK;
 }
 
@@ -980,7 +1082,20 @@ int launch_attn_sm100(const xdit_attn_params& p, cudaStream_t stream) {
   a.status_host = p.status_host;
   a.wait_limit_ns = p.wait_limit_ns ? p.wait_limit_ns : kWaitLimitNs;
   a.selftest_stall = p.selftest_stall;
-  dim3 grid((a.q_chunks + 3) / 4, p.H, p.B);
+  a.pairs = (a.q_chunks + 3) / 4;
+  a.kv_splits = 1;
+  a.part_rows = (int64_t)p.B * p.H * a.sq_total;
+  if (p.split_scratch && p.split_scratch_bytes > 0 && (((uintptr_t)p.split_scratch) & 15) == 0 && p.D % 4 == 0) {
+    int sms = 0;
+    if (check_device(&sms) == XDIT_OK && sms > 0) {
+      a.kv_splits = choose_kv_splits(p, sms, a.n_kv_tiles, a.pairs * p.H * p.B, a.part_rows, p.split_scratch_bytes);
+      if (a.kv_splits > 1) {
+        a.part_o = reinterpret_cast<float*>(p.split_scratch);
+        a.part_lse = a.part_o + (int64_t)a.kv_splits * a.part_rows * p.D;
+      }
+    }
+  }
+  dim3 grid(a.pairs * a.kv_splits, p.H, p.B);
   const bool bf16 = p.dtype == XDIT_BF16;
   if (p.D <= 64) {
     return bf16 ? launch_inst<1, 8, true>(a, grid, stream) : launch_inst<1, 8, false>(a, grid, stream);
@@ -988,6 +1103,16 @@ int launch_attn_sm100(const xdit_attn_params& p, cudaStream_t stream) {
   return bf16 ? launch_inst<2, 5, true>(a, grid, stream) : launch_inst<2, 5, false>(a, grid, stream);
 }
 
+int64_t attn_sm100_split_scratch_bytes(const xdit_attn_params& p) {
+  int sms = 0;
+  if (check_device(&sms) != XDIT_OK || sms <= 0) return 0;
+  const int q_cps = (p.q.seg_len + kChunk - 1) / kChunk, q_chunks = q_cps * p.q.nseg;
+  const int k_cps = (p.k.seg_len + kChunk - 1) / kChunk;
+  const int kv_chunks = k_cps * p.k.nseg + (p.k2.ptr ? (p.k2.seg_len + kChunk - 1) / kChunk : 0);
+  const int64_t part_rows = (int64_t)p.B * p.H * p.q.nseg * p.q.seg_len;
+  const int splits = choose_kv_splits(p, sms, (kv_chunks + 1) / 2, ((q_chunks + 3) / 4) * p.H * p.B, part_rows, -1);
+  return splits > 1 ? (int64_t)splits * part_rows * (p.D + 1) * 4 : 0;
+}
 
 }  // namespace xdit
 

@@ -471,6 +471,12 @@ int xdit_attn_which(const struct xdit_attn_params* p) {
   return attn_sm100_applicable(*p);
 }
 
+int64_t xdit_attn_split_scratch_bytes(const struct xdit_attn_params* p) {
+  if (!p || attn_check(p) != XDIT_OK) return 0;
+  if (p->force_generic || p->acc_in || p->acc_out || attn_sm100_applicable(*p) != 1) return 0;
+  return attn_sm100_split_scratch_bytes(*p);
+}
+
 int xdit_attn_fwd(const struct xdit_attn_params* p, void* stream) {
   int rc = attn_check(p);
   if (rc) return rc;

@@ -56,6 +56,8 @@ int launch_attn_generic(const xdit_attn_params& p, cudaStream_t stream);
 // Returns 1 when the tcgen05 kernel accepts p, 0 when it does not (reason in set_error).
 int attn_sm100_applicable(const xdit_attn_params& p);
 int launch_attn_sm100(const xdit_attn_params& p, cudaStream_t stream);
+// Scratch bytes with which launch_attn_sm100 may split the keys of p over several CTAs (0: it would not).
+int64_t attn_sm100_split_scratch_bytes(const xdit_attn_params& p);
 
 // ---- attention prologue (prologue.cu) ------------------------------------------------------------
 int launch_prologue(const xdit_prologue_params& p, cudaStream_t stream);

@@ -147,6 +147,42 @@ def _attn_params(q, k, v, k2, v2, out, lse, o_acc, lse_acc, acc_in, acc_out, cau
     return p
 
 
+# False: never hand out scratch, so that no call splits its keys (an A/B switch for measurements)
+SPLIT_KEYS = True
+_split_scratch = {}  # device index -> uint8 tensor reused by every call that splits its keys over CTAs
+
+
+def _give_split_scratch(p, q) -> None:
+    """Hand ``xdit_attn_fwd`` the scratch it wants for splitting a small launch's keys over several CTAs
+    (``xdit_attn_split_scratch_bytes``; nothing for most calls).  The buffer is kept per device and grows on
+    demand, but never while a stream is being captured: a call whose first run is a captured one simply is
+    not split."""
+    with torch.cuda.device(q.device):
+        need = int(_capi.load().xdit_attn_split_scratch_bytes(C.byref(p)))
+    if need <= 0:
+        return
+    key = q.device.index if q.device.index is not None else torch.cuda.current_device()
+    buf = _split_scratch.get(key)
+    if buf is None or buf.numel() < need:
+        if torch.cuda.is_current_stream_capturing():
+            if buf is None:
+                return
+        else:
+            buf = _split_scratch[key] = torch.empty(need, dtype=torch.uint8, device=q.device)
+    p.split_scratch = buf.data_ptr()
+    p.split_scratch_bytes = buf.numel()
+
+
+def attn_split_scratch_bytes(q, k, v, k2=None, v2=None) -> int:
+    """Scratch the library wants for splitting this call's keys over several CTAs (0: it would not split);
+    ``attn_fwd`` provides it by itself, this is for callers of the C ABI and for tests."""
+    _require_cuda(q, k, v, k2, v2)
+    out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+    p = _attn_params(q, k, v, k2, v2, out, None, None, None, False, False, False, None, False)
+    with torch.cuda.device(q.device):
+        return int(_capi.load().xdit_attn_split_scratch_bytes(C.byref(p)))
+
+
 def _launch_attn(fn, p, q, where):
     """Call an attention entry point; a timeout reported by an earlier launch surfaces here, and the
     status words are cleared so that the caller may retry."""
@@ -199,6 +235,8 @@ def attn_fwd(q, k, v, k2=None, v2=None, *, out=None, lse=None, o_acc=None, lse_a
         p.out = None
         p.out_stride_b, p.out_stride_h, p.out_stride_row = (int(x) for x in out_strides)
         p.out_stride_seg = 0
+    if not acc_in and not acc_out and not force_generic and not _selftest_stall and SPLIT_KEYS:
+        _give_split_scratch(p, q)
     _launch_attn(_capi.load().xdit_attn_fwd, p, q, "xdit_attn_fwd")
     launch_count += 1
     return out, lse
