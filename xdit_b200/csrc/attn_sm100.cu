@@ -975,7 +975,10 @@ __global__ void __launch_bounds__(256) split_merge_kernel(const __grid_constant_
 }
 
 // How many CTAs per pair of query tiles the keys of a call are split over: as many as fit the GPU's SMs
-// beside each other, at most 4, every split at least 4 key tiles long, and only what the scratch can hold.
+// beside each other (one wave), at most 4, every split at least four key tiles long, and only what the
+// scratch can hold.  54 CTAs (a Flux shard at Ulysses degree 8) become 108 of half the length.  Launches of
+// more than one wave are left alone: 216 CTAs (two waves) as 432 halves in three short waves measured
+// slower (149 against 138 us), the partial results' traffic and the merge eat the gain.
 int choose_kv_splits(const xdit_attn_params& p, int sms, int n_kv_tiles, int ctas, int64_t part_rows, int64_t scratch_bytes) {
   if (p.acc_in || p.acc_out || ctas <= 0) return 1;
   int want = sms / ctas;
