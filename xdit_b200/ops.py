@@ -156,7 +156,9 @@ def _give_split_scratch(p, q) -> None:
     """Hand ``xdit_attn_fwd`` the scratch it wants for splitting a small launch's keys over several CTAs
     (``xdit_attn_split_scratch_bytes``; nothing for most calls).  The buffer is kept per device and grows on
     demand, but never while a stream is being captured: a call whose first run is a captured one simply is
-    not split."""
+    not split.  One buffer per device: calls that split must not run at the same time on two streams of one
+    device (nothing in this package does that; a caller who does sets ``SPLIT_KEYS = False`` or passes scratch
+    of its own through the C ABI)."""
     with torch.cuda.device(q.device):
         need = int(_capi.load().xdit_attn_split_scratch_bytes(C.byref(p)))
     if need <= 0:
