@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define XDIT_ABI_VERSION 2
+#define XDIT_ABI_VERSION 3
 
 #if defined(__GNUC__)
 #define XDIT_API __attribute__((visibility("default")))

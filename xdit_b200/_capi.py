@@ -45,6 +45,9 @@ EXPORTS = [
 ]
 
 
+ABI_VERSION = 3  # XDIT_ABI_VERSION of include/xdit_b200.h: the structures below mirror that header
+
+
 class Caps(C.Structure):
     _fields_ = [
         ("abi_version", C.c_int), ("device", C.c_int), ("sm_major", C.c_int), ("sm_minor", C.c_int),
@@ -132,6 +135,11 @@ def load() -> C.CDLL:
     lib = C.CDLL(LIB_PATH)
     lib.xdit_query_caps.argtypes = [C.POINTER(Caps)]
     lib.xdit_query_caps.restype = C.c_int
+    caps = Caps()
+    lib.xdit_query_caps(C.byref(caps))  # the version is filled in before anything that needs a GPU
+    if caps.abi_version != ABI_VERSION:
+        raise RuntimeError(f"{LIB_PATH} has ABI version {caps.abi_version}, these bindings are written for "
+                           f"{ABI_VERSION}: rebuild it with `python -m xdit_b200.build --force`")
     lib.xdit_last_error_string.argtypes = []
     lib.xdit_last_error_string.restype = C.c_char_p
     lib.xdit_attn_fwd.argtypes = [C.POINTER(AttnParams), C.c_void_p]
