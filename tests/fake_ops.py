@@ -127,12 +127,86 @@ def seq_gather_unpad(recv, B, s, Cn, world, keep):
     return torch.from_numpy(np.ascontiguousarray(O.gather_and_unpad(chunks, world * s - keep, dim=1))).to(recv.dtype)
 
 
+# ---- peer-mapped buffers: POSIX shared memory stands for CUDA IPC, addresses are this process's own --------
+_shm = {}  # base address -> (SharedMemory, uint8 tensor over it, owner?)
+
+
+def _find(addr):
+    for base, (_, t, _) in _shm.items():
+        if base <= addr < base + t.numel():
+            return t, addr - base
+    raise KeyError(f"address {addr:#x} is not inside a mapped peer buffer")
+
+
+def peer_alloc(nbytes, device):
+    from multiprocessing import shared_memory
+
+    shm = shared_memory.SharedMemory(create=True, size=int(nbytes))
+    t = torch.frombuffer(shm.buf, dtype=torch.uint8, count=int(nbytes))
+    t.zero_()
+    _shm[t.data_ptr()] = (shm, t, True)
+    return t.data_ptr(), shm.name.encode().ljust(64, b"\0"), t
+
+
+def peer_open(handle, device):
+    from multiprocessing import shared_memory
+
+    shm = shared_memory.SharedMemory(name=bytes(handle).rstrip(b"\0").decode())
+    t = torch.frombuffer(shm.buf, dtype=torch.uint8, count=shm.size)
+    _shm[t.data_ptr()] = (shm, t, False)
+    return t.data_ptr()
+
+
+def peer_close(ptr):
+    shm, t, _ = _shm.pop(int(ptr))
+    del t
+    try:
+        shm.close()
+    except BufferError:  # a view handed out earlier is still alive: the mapping goes with the process
+        pass
+
+
+def peer_free(ptr):
+    shm, t, _ = _shm.pop(int(ptr))
+    del t
+    try:
+        shm.close()
+    except BufferError:
+        pass
+    shm.unlink()
+
+
+def peer_copy(dst_ptr, src, nbytes):
+    t, off = _find(int(dst_ptr))
+    t[off:off + nbytes].copy_(src.contiguous().view(torch.uint8).reshape(-1)[:nbytes])
+
+
+def peer_barrier(peer_flags, local_flags, epoch, rank, device, wait_limit_ns=0):
+    """The flag protocol of ``xdit_peer_barrier`` with host loads and stores: bump the epoch, store it into
+    word ``rank`` of every rank's flag array, wait until every word of the own array has reached it."""
+    import time
+
+    e = int(epoch.item()) + 1
+    epoch.fill_(e)
+    for p in peer_flags:
+        t, off = _find(int(p) + 4 * rank)
+        t[off:off + 4].view(torch.int32)[0] = e
+    mine, off = _find(int(local_flags))
+    words = mine[off:off + 4 * len(peer_flags)].view(torch.int32)
+    t0 = time.time()
+    while int(words.min()) < e:
+        if time.time() - t0 > 60:
+            raise RuntimeError(f"peer barrier {e}: flags {words.tolist()} after 60 s")
+        time.sleep(0.0005)
+
+
 def install(monkeypatch_or_none=None):
     """Replace the CUDA wrappers of ``xdit_b200.ops`` with the CPU stand-ins above."""
     import xdit_b200.ops as ops
 
     names = ["attn_fwd", "ulysses_pack", "ulysses_unpack_in", "ulysses_pack_out", "ulysses_unpack_out",
-             "kv_patch_update", "merge_out_lse", "qk_norm_rope_pack", "seq_shard_pad", "seq_gather_unpad"]
+             "kv_patch_update", "merge_out_lse", "qk_norm_rope_pack", "seq_shard_pad", "seq_gather_unpad",
+             "peer_alloc", "peer_open", "peer_close", "peer_free", "peer_copy", "peer_barrier"]
     for n in names:
         if monkeypatch_or_none is not None:
             monkeypatch_or_none.setattr(ops, n, globals()[n])

@@ -10,14 +10,14 @@ import os
 from tests.usp_worker import HERE, golden_files, run, run_flux_joint, run_kv, run_prologue
 
 
-@pytest.mark.parametrize("mode", ["usp", "legacy", "compat", "yunchang", "usp_pipelined"])
+@pytest.mark.parametrize("mode", ["usp", "legacy", "compat", "yunchang", "usp_pipelined", "usp_peer"])
 def test_world2_matches_reference(mode):
-    run(2, golden_files(2), mode, 29720 + ["usp", "legacy", "compat", "yunchang", "usp_pipelined"].index(mode))
+    run(2, golden_files(2), mode, 29720 + ["usp", "legacy", "compat", "yunchang", "usp_pipelined", "usp_peer"].index(mode))
 
 
-@pytest.mark.parametrize("mode", ["usp", "legacy", "yunchang", "usp_pipelined"])
+@pytest.mark.parametrize("mode", ["usp", "legacy", "yunchang", "usp_pipelined", "usp_peer"])
 def test_world4_matches_reference(mode):
-    run(4, golden_files(4), mode, 29730 + ["usp", "legacy", "yunchang", "usp_pipelined"].index(mode))
+    run(4, golden_files(4), mode, 29730 + ["usp", "legacy", "yunchang", "usp_pipelined", "usp_peer"].index(mode))
 
 
 def _need_reference():

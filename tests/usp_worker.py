@@ -58,7 +58,10 @@ def worker(rank, world, port, files, mode, errq, backend="gloo", dtype_name="flo
                 out = xdit_b200.USP(ql, kl, vl, **kw)
                 out2 = xdit_b200.USP(ql, kl, vl, **kw)  # second call: other result slot, same receive buffer
                 assert torch.equal(out, out2)
+                if R > 1:
+                    assert peer_exchange._exchanges, "the ring did not go through the peer buffers"
                 peer_exchange.enable(False)
+                peer_exchange.close_all()  # every rank: the buffers of this fixture's groups are released
             elif mode == "usp_pipelined":
                 # the same call with the head-group pipeline forced on (it is size-gated in production)
                 import xdit_b200.usp as _usp_mod

@@ -72,7 +72,8 @@ class PeerExchange:
         self.ptr, handle, self.local = ops.peer_alloc(total, self.device)
         self.local[self.flag_off:].zero_()
         self._epoch = torch.zeros(1, dtype=torch.int32, device=self.device)
-        torch.cuda.synchronize(self.device)
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
         handles: List[Optional[bytes]] = [None] * self.world
         dist.all_gather_object(handles, handle, group=group)
         self.peer_ptr = [self.ptr if r == self.rank else ops.peer_open(handles[r], self.device)
@@ -107,7 +108,8 @@ class PeerExchange:
                          self.rank, self.device)
 
     def close(self) -> None:
-        torch.cuda.synchronize(self.device)
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
         dist.barrier(group=self.group)
         for r, p in enumerate(self.peer_ptr):
             if r != self.rank:

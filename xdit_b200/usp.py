@@ -184,7 +184,7 @@ def _ring_native(q, kv_buf, kv_views, joint_k, joint_v, front, out, group, scale
     sq = q.shape[2] if q.dim() == 4 else q.shape[2] * q.shape[3]
     o_acc = torch.empty(B, Hl, sq, D, dtype=torch.float32, device=q.device)
     lse_acc = torch.empty(B, Hl, sq, dtype=torch.float32, device=q.device)
-    if q.is_cuda and not causal and kv_buf.is_contiguous():
+    if not causal and kv_buf.is_contiguous():
         from . import peer_exchange
 
         if peer_exchange.ring_enabled():
