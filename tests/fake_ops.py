@@ -24,7 +24,8 @@ FAST_FP32 = False  # large shapes: torch's fp32 CPU attention instead of the flo
 
 
 def attn_fwd(q, k, v, k2=None, v2=None, *, out=None, lse=None, o_acc=None, lse_acc=None, acc_in=False,
-             acc_out=False, causal=False, scale=None, force_generic=False, want_lse=False, **_):
+             acc_out=False, causal=False, scale=None, force_generic=False, want_lse=False, out_segments=None,
+             out_strides=None, **_):
     q4, k4, v4 = _flat4(q), _flat4(k), _flat4(v)
     if k2 is not None:
         k4 = torch.cat([k4, k2], dim=2)
@@ -40,6 +41,17 @@ def attn_fwd(q, k, v, k2=None, v2=None, *, out=None, lse=None, o_acc=None, lse_a
         o_acc.copy_(torch.from_numpy(o).to(o_acc.dtype))
         lse_acc.copy_(torch.from_numpy(l).to(lse_acc.dtype))
         return out, lse
+    if out_segments is not None:
+        # rows of query segment g go to the address out_segments[g] (a mapped peer buffer), laid out with the
+        # given (batch, head, row) element strides
+        B, H, G, L, D = q.shape if q.dim() == 5 else (q.shape[0], q.shape[1], 1, q.shape[2], q.shape[3])
+        res = torch.from_numpy(o).to(q.dtype).reshape(B, H, G, L, D)
+        es = q.element_size()
+        for g in range(G):
+            t, off = _find(int(out_segments[g]))
+            typed = t[off:off + (t.numel() - off) // es * es].view(q.dtype)
+            typed.as_strided((B, H, L, D), (*[int(x) for x in out_strides], 1)).copy_(res[:, :, g])
+        return None, lse
     if out is None:
         out = torch.empty(q.shape, dtype=q.dtype)
     out.copy_(torch.from_numpy(o).to(q.dtype).reshape(out.shape))
@@ -64,6 +76,22 @@ def ulysses_pack(items, U, head_group=None):
         for p in range(U):
             part = x[:, p * Hl + g * Hg:p * Hl + (g + 1) * Hg].permute(1, 0, 2, 3).reshape(-1)
             dst[p * stride:p * stride + blk].copy_(part)
+
+
+def ulysses_pack_peers(items, U, peer_base):
+    """The pack with peer p's block stored at the address peer_base[p] + dst_offset elements."""
+    for it in items:
+        src, joint, off = it["src"], it.get("joint"), int(it["dst_offset"])
+        x = src
+        if joint is not None:
+            x = torch.cat([joint, src], 2) if it.get("front") else torch.cat([src, joint], 2)
+        B, H, rows, D = x.shape
+        Hl = H // U
+        es = x.element_size()
+        for p in range(U):
+            part = x[:, p * Hl:(p + 1) * Hl].permute(1, 0, 2, 3).reshape(-1).contiguous()
+            t, boff = _find(int(peer_base[p]) + off * es)
+            t[boff:boff + part.numel() * es].copy_(part.view(torch.uint8))
 
 
 def ulysses_unpack_in(recv, B, Hl, s, D, U):
@@ -206,7 +234,7 @@ def install(monkeypatch_or_none=None):
 
     names = ["attn_fwd", "ulysses_pack", "ulysses_unpack_in", "ulysses_pack_out", "ulysses_unpack_out",
              "kv_patch_update", "merge_out_lse", "qk_norm_rope_pack", "seq_shard_pad", "seq_gather_unpad",
-             "peer_alloc", "peer_open", "peer_close", "peer_free", "peer_copy", "peer_barrier"]
+             "peer_alloc", "peer_open", "peer_close", "peer_free", "peer_copy", "peer_barrier", "ulysses_pack_peers"]
     for n in names:
         if monkeypatch_or_none is not None:
             monkeypatch_or_none.setattr(ops, n, globals()[n])

@@ -90,6 +90,14 @@ def test_flux_joint_fp32_case_at_full_size_two_ranks():
     run_flux_joint(2, 29761, tol=2e-5)
 
 
+@pytest.mark.parametrize("world", [2, 4])
+def test_peer_store_exchange_in_bf16(world):
+    """bf16 fixtures take the Ulysses exchange by stores into the peers' buffers (pack to per-peer bases, the
+    attention's rows to per-segment bases) and the ring rotation through peer slots, with shared memory for
+    the mapped buffers; compared with the reference's output for the bf16-rounded inputs."""
+    run(world, golden_files(world), "usp_peer", 29790 + world, dtype_name="bfloat16", tol=2e-2)
+
+
 def test_kv_views_over_a_slot_of_a_larger_buffer():
     """The ring hands the view builder a slice of a peer-mapped buffer (slot 0 or 1): the views must address
     the slice, not the start of the storage it lives in."""

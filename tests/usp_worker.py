@@ -61,6 +61,8 @@ def worker(rank, world, port, files, mode, errq, backend="gloo", dtype_name="flo
                 if R > 1:
                     assert peer_exchange._exchanges, "the ring did not go through the peer buffers"
                 peer_exchange.enable(False)
+                out = out.clone()  # the result is a view of a peer buffer, which goes away next
+                del out2
                 peer_exchange.close_all()  # every rank: the buffers of this fixture's groups are released
             elif mode == "usp_pipelined":
                 # the same call with the head-group pipeline forced on (it is size-gated in production)

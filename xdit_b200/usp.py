@@ -578,7 +578,7 @@ def usp_native(query, key, value, joint_query, joint_key, joint_value, joint_str
         assert H % U == 0, "h must be divisible by world_size, got {} and {}".format(H, U)
         Hl = H // U
         q_blk, kv_blk = Hl * B * sq * D, Hl * B * sk * D
-        if (R == 1 and not attn_layer and not want_lse and not is_causal and query.is_cuda
+        if (R == 1 and not attn_layer and not want_lse and not is_causal
                 and dt in (torch.bfloat16, torch.float16) and D % 8 == 0 and D <= 128 and U <= 16):
             from . import peer_exchange
 
