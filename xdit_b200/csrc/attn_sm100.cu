@@ -1,7 +1,10 @@
 // Flash-attention forward for sm_100a: tcgen05.mma with TMEM accumulators, operands staged by
 // TMA, warp-specialised online softmax.  bf16/fp16, head_dim a multiple of 8 up to 128.
 //
-// One CTA owns two query tiles of 128 rows and walks all key/value tiles of 128 rows.
+// One CTA owns two query tiles of 128 rows and walks all key/value tiles of 128 rows -- or, when the
+// launch is too small to fill the GPU, its share of them: the keys are then split over several CTAs per
+// pair of query tiles, every CTA writes a normalised fp32 partial result with its log-sum-exp, and
+// split_merge_kernel combines the partials into the output.
 //   warps 0-3  softmax group for query tile 0   (one thread per query row)
 //   warps 4-7  softmax group for query tile 1
 //   warp  8    issues every tcgen05.mma (the warp runs converged, one elected lane issues) and owns
