@@ -98,6 +98,12 @@ def test_peer_store_exchange_in_bf16(world):
     run(world, golden_files(world), "usp_peer", 29790 + world, dtype_name="bfloat16", tol=2e-2)
 
 
+def test_peer_buffers_grow_collectively():
+    from tests.usp_worker import run_peer_growth
+
+    run_peer_growth(2, 29797)
+
+
 def test_kv_views_over_a_slot_of_a_larger_buffer():
     """The ring hands the view builder a slice of a peer-mapped buffer (slot 0 or 1): the views must address
     the slice, not the start of the storage it lives in."""

@@ -441,6 +441,70 @@ def run(world, files, mode, port, **kw):
     assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
 
 
+
+def peer_growth_worker(rank, world, port, errq):
+    """The peer buffers of one process group are re-allocated (collectively) when a later call needs more
+    room; results of the small and the large call must equal the NCCL path's before and after the growth,
+    for the Ulysses exchange by stores and for the ring rotation through peer slots."""
+    try:
+        sys.path.insert(0, ROOT)
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        torch.set_num_threads(1)
+        import xdit_b200
+        from tests import fake_ops
+        from xdit_b200 import peer_exchange
+
+        fake_ops.install()
+        for U, R in ((world, 1), (1, world)):
+            xdit_b200.init_sequence_parallel(U, R, backend="gloo")
+            g = torch.Generator().manual_seed(5)
+            data = {}
+            for S in (64, 256):
+                q, k, v = (torch.randn(1, 4, S, 16, generator=g).to(torch.bfloat16) for _ in range(3))
+                data[S] = tuple(t.chunk(world, dim=2)[rank].contiguous() for t in (q, k, v))
+            want = {S: xdit_b200.USP(*data[S]).clone() for S in data}
+            peer_exchange.enable(True)
+            sizes = []
+            for S in (64, 256, 64, 256):  # the second call grows the buffers, the third runs in the grown ones
+                got = xdit_b200.USP(*data[S]).clone()
+                assert peer_exchange._exchanges, "the call did not go through the peer buffers"
+                sizes.append(max(ex.out_bytes for ex in peer_exchange._exchanges.values()))
+                err = float((got.float() - want[S].float()).abs().max())
+                assert err <= 2e-2, (U, R, S, err)
+            assert sizes[1] > sizes[0] and sizes[2] == sizes[1] == sizes[3], sizes
+            peer_exchange.enable(False)
+            peer_exchange.close_all()
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception as e:
+        import traceback
+
+        errq.put(f"rank {rank}: {e}\n{traceback.format_exc()}")
+        raise
+
+
+def run_peer_growth(world, port):
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    errq = ctx.SimpleQueue()
+    procs = [ctx.Process(target=peer_growth_worker, args=(r, world, port, errq)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+    msgs = []
+    while not errq.empty():
+        msgs.append(errq.get())
+    alive = [p for p in procs if p.is_alive()]
+    for p in alive:
+        p.terminate()
+    assert not msgs, "\n".join(msgs)
+    assert not alive, "ranks did not finish"
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+
 def golden_files(world):
     import glob
 
