@@ -22,7 +22,9 @@ N > 1 is launched by ``torch.distributed.run`` (one rank per GPU, NCCL); the seq
 over N ranks (strong scaling) with Ulysses degree N, which is the fastest split behind NVSwitch;
 ``--sp ULYSSESxRING`` selects another split, e.g. ``--sp 2x4`` for Ulysses 2 x ring 4, the split the
 Wan2.1 workload is usually quoted with.  Ring splits are also measured (and checked) as legs under
-``extra``.
+``extra``, with the K/V rotation by copy-engine transfers into the next rank's buffer and over NCCL
+send/recv; the Ulysses exchange runs by stores into the peers' memory (``--exchange peer``, the default,
+kept only if a probing call succeeds on every rank) with the NCCL form as a leg.
 
 ``--impl reference`` times the reference's own ``USP()`` (its unmodified Python, taken from
 ``oracle/_ref``) on the host cores of rank 0, on a bounded sample of the same workload; without
